@@ -34,6 +34,9 @@ struct GenericAttnArgs {
   const float* slopes;                         // [n_q_heads] or null: slope * (key position - query position) is added to the scores
   int shared_kv;                               // 1: a page holds one vector per token that is key and value at once ([page][1][kv_head][slot][hd])
   const void* gate; long long gate_stride;     // [n_tokens, n_q_heads] or null: head h's output is multiplied by sigmoid(gate[t, h])
+  int chunk;                                   // > 0: a query at position p sees the keys from p - p % chunk on (its own chunk of positions)
+  const float* log_r1; const float* log_r2;    // [n_q_heads] or null: r1 * log(1 + r2 * (query position - key position)) is taken off the scores
+  const float* sinks;                          // [n_q_heads] or null: exp(sink) joins the softmax's denominator, without a key or a value
 };
 
 template <typename T>
@@ -47,7 +50,8 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
   const int kvh = head / (a.n_q_heads / a.n_kv_heads);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = a.positions[t];
-  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  if (a.chunk > 0) lo = max(lo, pos - pos % a.chunk);
   const int* table = a.block_table + (size_t)a.token_seq[t] * a.max_blocks;
 
   const T* q = (const T*)a.q + (size_t)t * a.q_stride + (size_t)head * hd;
@@ -78,6 +82,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
         s = dot * a.scale;
         if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
         if (a.slopes) s = fmaf(a.slopes[head], (float)(key - pos), s);
+        if (a.log_r1) s -= a.log_r1[head] * logf(1.0f + a.log_r2[head] * (float)(pos - key));
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -111,7 +116,9 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
 
   float M = part_m[0];
   for (int w = 1; w < kWarps; ++w) M = fmaxf(M, part_m[w]);
-  float L = 0.f;
+  const float sink = a.sinks ? a.sinks[head] : -INFINITY;
+  M = fmaxf(M, sink);
+  float L = a.sinks ? expf(sink - M) : 0.f;
   float f[kWarps];
   for (int w = 0; w < kWarps; ++w) {
     f[w] = part_m[w] == -INFINITY ? 0.f : expf(part_m[w] - M);
@@ -135,12 +142,16 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
 // shared_kv = 1: the cache holds one vector per token and kv head, [page][1][kv_head][slot][head_dim], which is read as
 // the key and as the value (attention over a cached low-rank vector).  gate ([n_tokens, n_q_heads] of `dtype`, row stride
 // gate_stride, may be null): head h's output of token t is multiplied by sigmoid(gate[t, h]).
-LMSF_API int lmsf_attention_generic_ext(const void* q, long long q_stride, void* out, long long out_stride,
-                                        const void* cache, long long page_stride, const int* block_table, int max_blocks,
-                                        int block_size, const int* token_seq, const int* positions, float scale,
-                                        float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
-                                        int n_kv_heads, int head_dim, int dtype, int shared_kv, const void* gate,
-                                        long long gate_stride, void* stream) {
+// chunk > 0: a query at position p sees only the keys of its own chunk of positions, p - p % chunk .. p (chunks are counted
+// from position 0 of the request).  log_r1, log_r2 ([n_q_heads] float32, both or neither): r1 * log(1 + r2 * distance) is
+// taken off the scaled score.  sinks ([n_q_heads] float32 or null): exp(sink[head]) is one more term of the denominator.
+LMSF_API int lmsf_attention_generic_masked(const void* q, long long q_stride, void* out, long long out_stride,
+                                           const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                           int block_size, const int* token_seq, const int* positions, float scale,
+                                           float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
+                                           int n_kv_heads, int head_dim, int dtype, int shared_kv, const void* gate,
+                                           long long gate_stride, int chunk, const float* log_r1, const float* log_r2,
+                                           const float* sinks, void* stream) {
   using namespace lmsf;
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % 16)
@@ -150,14 +161,26 @@ LMSF_API int lmsf_attention_generic_ext(const void* q, long long q_stride, void*
   if (n_q_heads > 65535) LMSF_REFUSE("attention: more than 65535 query heads");
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention: bad block table geometry");
   if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("attention: unknown dtype code %d", dtype);
+  if ((log_r1 == nullptr) != (log_r2 == nullptr)) LMSF_REFUSE("attention: the logarithmic bias needs both of its constants");
   GenericAttnArgs a{q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
                     token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim, softcap > 0.f ? softcap : 0.f, slopes,
-                    shared_kv ? 1 : 0, gate, gate_stride};
+                    shared_kv ? 1 : 0, gate, gate_stride, chunk > 0 ? chunk : 0, log_r1, log_r2, sinks};
   dim3 grid(n_tokens, n_q_heads);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == LMSF_F32) attention_generic_kernel<float><<<grid, kWarps * 32, 0, s>>>(a);
   else attention_generic_kernel<bf16><<<grid, kWarps * 32, 0, s>>>(a);
   return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_attention_generic_ext(const void* q, long long q_stride, void* out, long long out_stride,
+                                        const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                        int block_size, const int* token_seq, const int* positions, float scale,
+                                        float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
+                                        int n_kv_heads, int head_dim, int dtype, int shared_kv, const void* gate,
+                                        long long gate_stride, void* stream) {
+  return lmsf_attention_generic_masked(q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
+                                       token_seq, positions, scale, softcap, slopes, window, n_tokens, n_q_heads, n_kv_heads,
+                                       head_dim, dtype, shared_kv, gate, gate_stride, 0, nullptr, nullptr, nullptr, stream);
 }
 
 LMSF_API int lmsf_attention_generic_scores(const void* q, long long q_stride, void* out, long long out_stride,

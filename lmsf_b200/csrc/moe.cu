@@ -268,6 +268,27 @@ __global__ void moe_combine_kernel(TO* __restrict__ out, const TD* __restrict__ 
   }
 }
 
+// Gated experts whose routing weight multiplies what the expert READS: expert(w h) = (act(w g) * (w u)) W_down^T with
+// g = W_gate h and u = W_up h, because both products are linear in h.  The weight is applied here, in float32, to the
+// products of the unweighted token: y[r, 0:F] = g, y[r, F:2F] = u for row r of the pair (token, choice); out[r, i] =
+// act(w g_i) * (w u_i).  ACT 0: silu, 1: the tanh form of gelu.  One block per pair; weights null: w = 1.
+template <typename T, int ACT>
+__global__ void moe_weighted_glu_kernel(T* __restrict__ out, const T* __restrict__ y, const int* __restrict__ pair_row,
+                                        const float* __restrict__ wts, int F) {
+  const int pair = blockIdx.x;
+  const int row = pair_row[pair];
+  if (row < 0) return;
+  const float w = wts ? wts[pair] : 1.0f;
+  const T* yr = y + (size_t)row * 2 * F;
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    const float g = w * to_f32(yr[i]), u = w * to_f32(yr[F + i]);
+    float a;
+    if (ACT == 0) a = g / (1.0f + expf(-g));
+    else a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    out[(size_t)row * F + i] = from_f32<T>(a * u);
+  }
+}
+
 template <typename T>
 __global__ void relu2_kernel(T* __restrict__ x, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -358,5 +379,22 @@ LMSF_API int lmsf_relu2(void* x, long long n, int dtype, void* stream) {
   if (dtype == LMSF_F32) relu2_kernel<float><<<blocks, 256, 0, s>>>((float*)x, n);
   else if (dtype == LMSF_BF16) relu2_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)x, n);
   else LMSF_REFUSE("relu2: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}
+
+// out: [pairs, F]; y: [pairs, 2 F] (gate | up) of `dtype`, rows in expert order; pair_row: [pairs] row of every (token,
+// choice) pair; wts: float32 [pairs] or null.  act: 0 silu, 1 gelu (tanh form).
+LMSF_API int lmsf_moe_weighted_glu(void* out, const void* y, const int* pair_row, const float* wts, int pairs, int F, int act,
+                                   int dtype, void* stream) {
+  using namespace lmsf;
+  if (pairs <= 0) return 0;
+  if (F <= 0 || (act != 0 && act != 1)) LMSF_REFUSE("moe: F=%d act=%d", F, act);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = F >= 256 ? 256 : 128;
+#define LMSF_GO(T, A) moe_weighted_glu_kernel<T, A><<<pairs, threads, 0, s>>>((T*)out, (const T*)y, pair_row, wts, F)
+  if (dtype == LMSF_F32) { if (act) LMSF_GO(float, 1); else LMSF_GO(float, 0); }
+  else if (dtype == LMSF_BF16) { if (act) LMSF_GO(bf16, 1); else LMSF_GO(bf16, 0); }
+  else LMSF_REFUSE("moe: unknown dtype code %d", dtype);
+#undef LMSF_GO
   return LMSF_LAUNCH_STATUS();
 }

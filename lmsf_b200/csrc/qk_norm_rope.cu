@@ -23,6 +23,8 @@ struct QkNormRopeArgs {
   int n_q_heads, n_kv_heads, head_dim, norm_dim;
   const float* wq; const float* wk; float eps;
   int* error_flag;
+  int weightless;       // 1: q and k are divided by their root mean square although wq and wk are null (a norm without a weight)
+  int v_norm_dim;       // > 0: every value head is divided by the root mean square of its first v_norm_dim values before it is stored
 };
 
 constexpr int kWarps = 4;
@@ -62,7 +64,14 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_kernel(QkNormRopeArg
       const int g = head - a.n_q_heads - n_k;
       if (vc) {
         const T* src = (const T*)a.v + (size_t)t * a.v_stride + (size_t)g * hd;
-        for (int i = lane; i < hd; i += 32) vc[g * head_pitch + i] = src[i];
+        if (a.v_norm_dim > 0) {
+          float ss = 0.f;
+          for (int i = lane; i < a.v_norm_dim; i += 32) { const float x = to_f32(src[i]); ss = fmaf(x, x, ss); }
+          const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)a.v_norm_dim + a.eps);
+          for (int i = lane; i < hd; i += 32) vc[g * head_pitch + i] = i < a.v_norm_dim ? from_f32<T>(to_f32(src[i]) * inv) : src[i];
+        } else {
+          for (int i = lane; i < hd; i += 32) vc[g * head_pitch + i] = src[i];
+        }
       }
       continue;
     }
@@ -81,9 +90,9 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_kernel(QkNormRopeArg
     }
     ss = warp_sum(ss);
     __syncwarp();
-    if (w) {
+    if (w || a.weightless) {
       const float inv = 1.0f / sqrtf(ss / (float)a.norm_dim + a.eps);
-      for (int i = lane; i < a.norm_dim; i += 32) buf[i] = (buf[i] * inv) * w[i];
+      for (int i = lane; i < a.norm_dim; i += 32) buf[i] = w ? (buf[i] * inv) * w[i] : buf[i] * inv;
     }
     __syncwarp();
     for (int p = lane; p < half; p += 32) {
@@ -135,8 +144,23 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_vec_kernel(QkNormRop
   for (int head = warp + kWarps * blockIdx.y; head < a.n_q_heads + 2 * n_k; head += kWarps * gridDim.y) {
     if (head >= a.n_q_heads + n_k) {
       const int g = head - a.n_q_heads - n_k;
-      if (vc) *reinterpret_cast<Vec*>(vc + g * head_pitch + e0) =
-          *reinterpret_cast<const Vec*>((const T*)a.v + (size_t)t * a.v_stride + (size_t)g * hd + e0);
+      if (vc) {
+        Vec raw = *reinterpret_cast<const Vec*>((const T*)a.v + (size_t)t * a.v_stride + (size_t)g * hd + e0);
+        if (a.v_norm_dim > 0) {
+          float x[VW];
+          float ss = 0.f;
+#pragma unroll
+          for (int j = 0; j < VW; ++j) {
+            x[j] = to_f32(raw.v[j]);
+            if (e0 + j < a.v_norm_dim) ss = fmaf(x[j], x[j], ss);
+          }
+          const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)a.v_norm_dim + a.eps);
+#pragma unroll
+          for (int j = 0; j < VW; ++j)
+            if (e0 + j < a.v_norm_dim) raw.v[j] = from_f32<T>(x[j] * inv);
+        }
+        *reinterpret_cast<Vec*>(vc + g * head_pitch + e0) = raw;
+      }
       continue;
     }
     const bool is_q = head < a.n_q_heads;
@@ -155,11 +179,11 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_vec_kernel(QkNormRop
       if (e0 + j < a.norm_dim) ss = fmaf(x[j], x[j], ss);
     }
     ss = warp_sum(ss);
-    if (w) {
+    if (w || a.weightless) {
       const float inv = 1.0f / sqrtf(ss / (float)a.norm_dim + a.eps);
 #pragma unroll
       for (int j = 0; j < VW; ++j)
-        if (e0 + j < a.norm_dim) x[j] = (x[j] * inv) * w[e0 + j];
+        if (e0 + j < a.norm_dim) x[j] = w ? (x[j] * inv) * w[e0 + j] : x[j] * inv;
     }
 #pragma unroll
     for (int j = 0; j < VW; j += 2) {
@@ -179,25 +203,28 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_vec_kernel(QkNormRop
 }  // namespace lmsf
 
 // q: [n, n_q_heads * head_dim] (changed in place), k, v: [n, n_kv_heads * head_dim], rows of `dtype` with the given strides;
-// wq, wk: float32 [norm_dim] or null (no norm); inv_freq: float32 [rot_dim / 2] or null (no rotation); cache null: q only.
-LMSF_API int lmsf_qk_norm_rope_cache_write(void* q, const void* k, const void* v, long long q_stride, long long k_stride,
-                                           long long v_stride, const int* positions, const int* token_seq,
-                                           const int* block_table, int max_blocks, int block_size, void* cache,
-                                           long long page_stride, const float* inv_freq, int rot_dim, int is_neox,
-                                           int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, int norm_dim,
-                                           const float* wq, const float* wk, float eps, int dtype, int* error_flag,
-                                           void* stream) {
+// wq, wk: float32 [norm_dim] or null (no norm, or with `weightless` a norm without a weight); inv_freq: float32
+// [rot_dim / 2] or null (no rotation); cache null: q only.  v_norm_dim > 0: the value heads are normed too (no weight).
+LMSF_API int lmsf_qk_norm_rope_cache_write_unit(void* q, const void* k, const void* v, long long q_stride, long long k_stride,
+                                                long long v_stride, const int* positions, const int* token_seq,
+                                                const int* block_table, int max_blocks, int block_size, void* cache,
+                                                long long page_stride, const float* inv_freq, int rot_dim, int is_neox,
+                                                int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, int norm_dim,
+                                                const float* wq, const float* wk, float eps, int dtype, int* error_flag,
+                                                int weightless, int v_norm_dim, void* stream) {
   using namespace lmsf;
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || n_q_heads < 0 || n_kv_heads < 0 || norm_dim <= 0 || norm_dim > head_dim)
     LMSF_REFUSE("qk_norm_rope: head_dim=%d norm_dim=%d", head_dim, norm_dim);
   if (inv_freq && (rot_dim <= 0 || rot_dim % 2 || rot_dim > norm_dim))
     LMSF_REFUSE("qk_norm_rope: rot_dim=%d must be even and at most %d", rot_dim, norm_dim);
-  if ((wq || wk) && !(eps > 0.f)) LMSF_REFUSE("qk_norm_rope: eps must be positive");
+  if ((wq || wk || weightless || v_norm_dim > 0) && !(eps > 0.f)) LMSF_REFUSE("qk_norm_rope: eps must be positive");
+  if (v_norm_dim < 0 || v_norm_dim > head_dim) LMSF_REFUSE("qk_norm_rope: v_norm_dim=%d of head_dim=%d", v_norm_dim, head_dim);
   if (cache && (!k || !v || !block_table || !token_seq || block_size <= 0 || max_blocks <= 0))
     LMSF_REFUSE("qk_norm_rope: a cache write needs k, v, a block table and the block size");
   QkNormRopeArgs a{q, k, v, q_stride, k_stride, v_stride, positions, token_seq, block_table, max_blocks, block_size, cache,
-                   page_stride, inv_freq, rot_dim, is_neox, n_q_heads, n_kv_heads, head_dim, norm_dim, wq, wk, eps, error_flag};
+                   page_stride, inv_freq, rot_dim, is_neox, n_q_heads, n_kv_heads, head_dim, norm_dim, wq, wk, eps, error_flag,
+                   weightless ? 1 : 0, v_norm_dim};
   const size_t smem = ((inv_freq ? rot_dim : 0) + (size_t)kWarps * head_dim) * sizeof(float);
   if (smem > 48 * 1024) LMSF_REFUSE("qk_norm_rope: head_dim=%d is too wide", head_dim);
   cudaStream_t s = (cudaStream_t)stream;
@@ -221,4 +248,16 @@ LMSF_API int lmsf_qk_norm_rope_cache_write(void* q, const void* k, const void* v
   else if (dtype == LMSF_BF16) qk_norm_rope_kernel<bf16><<<n_tokens, kWarps * 32, smem, s>>>(a);
   else LMSF_REFUSE("qk_norm_rope: unknown dtype code %d", dtype);
   return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_qk_norm_rope_cache_write(void* q, const void* k, const void* v, long long q_stride, long long k_stride,
+                                           long long v_stride, const int* positions, const int* token_seq,
+                                           const int* block_table, int max_blocks, int block_size, void* cache,
+                                           long long page_stride, const float* inv_freq, int rot_dim, int is_neox,
+                                           int n_tokens, int n_q_heads, int n_kv_heads, int head_dim, int norm_dim,
+                                           const float* wq, const float* wk, float eps, int dtype, int* error_flag,
+                                           void* stream) {
+  return lmsf_qk_norm_rope_cache_write_unit(q, k, v, q_stride, k_stride, v_stride, positions, token_seq, block_table, max_blocks,
+                                            block_size, cache, page_stride, inv_freq, rot_dim, is_neox, n_tokens, n_q_heads,
+                                            n_kv_heads, head_dim, norm_dim, wq, wk, eps, dtype, error_flag, 0, 0, stream);
 }

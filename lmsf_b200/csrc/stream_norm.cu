@@ -195,6 +195,102 @@ static int pick_stream(float* res, const void* y, const float* w_post, const flo
   return LMSF_EBADARG;
 }
 
+
+// Two branches that read the same normed stream, each behind a gate of its own (a layer whose mixer and feed-forward run
+// side by side):  res <- res + sigmoid(z[:, 0:D] + b[0:D]) * y1 + sigmoid(z[:, D:2D] + b[D:2D]) * y2, then, if asked,
+// h = norm(res) * w_next for whoever reads the stream next.  z: float32 gate logits [n, D or 2 D] (row stride ldz), b:
+// float32 [D or 2 D] or null; y2 may be null (a layer without a feed-forward).  Sigmoid, products and sums are float32.
+template <typename T, int PER, int V>
+__global__ void __launch_bounds__(kThreads) gated_branches_kernel(float* __restrict__ res, const float* __restrict__ z,
+                                                                  long long ldz, const float* __restrict__ b,
+                                                                  const T* __restrict__ y1, const T* __restrict__ y2,
+                                                                  T* __restrict__ h, const float* __restrict__ w_next,
+                                                                  int hidden, float eps_next) {
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  const float* zr = z + (size_t)blockIdx.x * ldz;
+  float r[PER][V];
+  pdl_launch_dependents();
+  pdl_wait();
+  float s2 = 0.f;
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int i = (it * kThreads + threadIdx.x) * V;
+#pragma unroll
+    for (int e = 0; e < V; ++e) r[it][e] = 0.f;
+    if (i < hidden) {
+      ld_vec<V>(res + base + i, r[it]);
+      float g[V], c[V], y[V];
+      ld_vec<V>(zr + i, g);
+      if (b != nullptr) { ld_vec<V>(b + i, c);
+#pragma unroll
+        for (int e = 0; e < V; ++e) g[e] += c[e]; }
+      ld_vec<V>(y1 + base + i, y);
+#pragma unroll
+      for (int e = 0; e < V; ++e) r[it][e] = fmaf(1.0f / (1.0f + expf(-g[e])), y[e], r[it][e]);
+      if (y2 != nullptr) {
+        ld_vec<V>(zr + hidden + i, g);
+        if (b != nullptr) { ld_vec<V>(b + hidden + i, c);
+#pragma unroll
+          for (int e = 0; e < V; ++e) g[e] += c[e]; }
+        ld_vec<V>(y2 + base + i, y);
+#pragma unroll
+        for (int e = 0; e < V; ++e) r[it][e] = fmaf(1.0f / (1.0f + expf(-g[e])), y[e], r[it][e]);
+      }
+      st_vec<V>(res + base + i, r[it]);
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) s2 = fmaf(r[it][e], r[it][e], s2);
+  }
+  if (h == nullptr) return;
+  s2 = block_sum(s2, scratch);
+  const float inv = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int i = (it * kThreads + threadIdx.x) * V;
+    if (i < hidden) {
+      float wn[V], o[V];
+      ld_vec<V>(w_next + i, wn);
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = (r[it][e] * inv) * wn[e];
+      st_vec<V>(h + base + i, o);
+    }
+  }
+}
+
+// out[t] = [a[t] | b[t]] in the activation type: two float32 streams side by side as the input of one product.
+template <typename T>
+__global__ void stream_concat_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                     int hidden, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / (2 * hidden);
+  const int c = (int)(i % (2 * hidden));
+  out[i] = from_f32<T>(c < hidden ? a[t * hidden + c] : b[t * hidden + c - hidden]);
+}
+
+template <typename T, int PER, int V>
+static int launch_gated(float* res, const float* z, long long ldz, const float* b, const void* y1, const void* y2, void* h,
+                        const float* w_next, int n, int hidden, float eps_next, cudaStream_t s) {
+  return launch_pdl(gated_branches_kernel<T, PER, V>, dim3(n), dim3(kThreads), 0, s, res, z, ldz, b, (const T*)y1, (const T*)y2,
+                    (T*)h, w_next, hidden, eps_next);
+}
+
+template <typename T>
+static int pick_gated(float* res, const float* z, long long ldz, const float* b, const void* y1, const void* y2, void* h,
+                      const float* w_next, int n, int hidden, float eps_next, cudaStream_t s) {
+  const bool wide = hidden % 4 == 0 && ldz % 4 == 0 && ((uintptr_t)res | (uintptr_t)z | (uintptr_t)b | (uintptr_t)w_next) % 16 == 0 &&
+                    ((uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)h) % (4 * sizeof(T)) == 0;
+  const int per = ceil_div(hidden, kThreads * (wide ? 4 : 1));
+#define LMSF_CASE(P)                                                                                              \
+  if (per <= P) return wide ? launch_gated<T, P, 4>(res, z, ldz, b, y1, y2, h, w_next, n, hidden, eps_next, s)   \
+                            : launch_gated<T, P, 1>(res, z, ldz, b, y1, y2, h, w_next, n, hidden, eps_next, s)
+  LMSF_CASE(1); LMSF_CASE(2); LMSF_CASE(4); LMSF_CASE(8); LMSF_CASE(16);
+  if (!wide) { LMSF_CASE(32); LMSF_CASE(64); }
+#undef LMSF_CASE
+  return LMSF_EBADARG;
+}
+
 }  // namespace lmsf
 
 // res: float32 [n, hidden].  y ([n, hidden] of `dtype`, with float32 w_post [hidden] and optional float32 ls [hidden]),
@@ -245,5 +341,34 @@ LMSF_API int lmsf_stream_begin(float* res, const void* x, long long count, int d
   if (dtype == LMSF_F32) stream_begin_kernel<float><<<blocks, 256, 0, s>>>(res, (const float*)x, count);
   else if (dtype == LMSF_BF16) stream_begin_kernel<bf16><<<blocks, 256, 0, s>>>(res, (const bf16*)x, count);
   else LMSF_REFUSE("stream_begin: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}
+
+// res: float32 [n, hidden]; z: float32 [n, (y2 ? 2 : 1) * hidden] with row stride ldz; b: float32 of z's width or null; y1,
+// y2 (may be null), h (may be null; then w_next is not read): [n, hidden] of `dtype`.
+LMSF_API int lmsf_gated_branches(float* res, const float* z, long long ldz, const float* b, const void* y1, const void* y2,
+                                 void* h, const float* w_next, int n, int hidden, float eps_next, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (hidden <= 0 || hidden > kThreads * kMaxPerThread) LMSF_REFUSE("gated_branches: width %d is outside 1..%d", hidden, kThreads * kMaxPerThread);
+  if (!z || !y1 || ldz < (y2 ? 2 : 1) * (long long)hidden) LMSF_REFUSE("gated_branches: gate logits of %lld values a row for width %d", ldz, hidden);
+  if (h != nullptr && (w_next == nullptr || !(eps_next > 0.f))) LMSF_REFUSE("gated_branches: the next norm needs its weight and a positive eps");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) return pick_gated<float>(res, z, ldz, b, y1, y2, h, w_next, n, hidden, eps_next, s);
+  if (dtype == LMSF_BF16) return pick_gated<bf16>(res, z, ldz, b, y1, y2, h, w_next, n, hidden, eps_next, s);
+  LMSF_REFUSE("gated_branches: unknown dtype code %d", dtype);
+}
+
+// out: [n, 2 * hidden] of `dtype` = [a | b], both float32 [n, hidden].
+LMSF_API int lmsf_stream_concat(void* out, const float* a, const float* b, int n, int hidden, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (hidden <= 0) LMSF_REFUSE("stream_concat: width %d", hidden);
+  const long long count = 2LL * n * hidden;
+  const unsigned blocks = (unsigned)((count + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) stream_concat_kernel<float><<<blocks, 256, 0, s>>>((float*)out, a, b, hidden, count);
+  else if (dtype == LMSF_BF16) stream_concat_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, a, b, hidden, count);
+  else LMSF_REFUSE("stream_concat: unknown dtype code %d", dtype);
   return LMSF_LAUNCH_STATUS();
 }

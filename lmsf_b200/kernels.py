@@ -207,10 +207,13 @@ def qk_norm_rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Opti
                              token_seq: Optional[torch.Tensor], block_table: Optional[torch.Tensor], block_size: int,
                              cache: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rot_dim: int, is_neox: bool,
                              n_q_heads: int, n_kv_heads: int, head_dim: int, norm_dim: int, wq: Optional[torch.Tensor],
-                             wk: Optional[torch.Tensor], eps: float, error_flag: Optional[torch.Tensor] = None):
+                             wk: Optional[torch.Tensor], eps: float, error_flag: Optional[torch.Tensor] = None,
+                             weightless: bool = False, v_norm_dim: int = 0):
     """Per head: RMS norm of q and k over their first `norm_dim` values (float32 weights wq, wk [norm_dim]; None: no
-    norm), then the rotation of the first `rot_dim` values, then k and v into `cache` as `rope_cache_write` does; one
-    kernel, rounded once.  q is changed in place.  cache None: q only."""
+    norm, or with `weightless` a division by the root mean square alone), then the rotation of the first `rot_dim`
+    values, then k and v into `cache` as `rope_cache_write` does; one kernel, rounded once.  v_norm_dim > 0: every value
+    head is divided by the root mean square of its first v_norm_dim values on the way.  q is changed in place.  cache
+    None: q only."""
     n = q.shape[0]
     for name, t, heads in (("q", q, n_q_heads), ("k", k, n_kv_heads), ("v", v, n_kv_heads)):
         if t is None:
@@ -225,15 +228,16 @@ def qk_norm_rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Opti
         page_stride, max_blocks = cache.stride(0), block_table.shape[1]
     if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2):
         raise KernelError("qk_norm_rope: inv_freq must hold rot_dim / 2 float32 values")
-    f = _func("qk_norm_rope.cu", "lmsf_qk_norm_rope_cache_write",
+    f = _func("qk_norm_rope.cu", "lmsf_qk_norm_rope_cache_write_unit",
               [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-               c_float, c_int, c_void_p, c_void_p])
+               c_float, c_int, c_void_p, c_int, c_int, c_void_p])
     rc = f(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0) if k is not None else 0,
            v.stride(0) if v is not None else 0, _i32(positions, "positions"), _i32(token_seq, "token_seq"),
            _i32(block_table, "block_table"), max_blocks, block_size, _ptr(cache), page_stride, _ptr(inv_freq),
            rot_dim, int(is_neox), n, n_q_heads, n_kv_heads, head_dim, norm_dim, _f32vec(wq, norm_dim, "wq"),
-           _f32vec(wk, norm_dim, "wk"), float(eps), dtype_code(q.dtype), _i32(error_flag, "error_flag"), _stream())
+           _f32vec(wk, norm_dim, "wk"), float(eps), dtype_code(q.dtype), _i32(error_flag, "error_flag"), int(bool(weightless)),
+           int(v_norm_dim or 0), _stream())
     _check(rc, "qk_norm_rope.cu", "lmsf_qk_norm_rope")
 
 
@@ -242,29 +246,48 @@ def qk_norm_rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Opti
 GENERIC_MAX_HEAD_DIM = 512     # the plain attention kernel holds a head's accumulator in registers up to this size
 
 
+def _per_head(t: Optional[torch.Tensor], heads: int, what: str) -> None:
+    if t is not None and (t.dtype != torch.float32 or t.shape != (heads,) or not t.is_contiguous()):
+        raise KernelError(f"attention: {what} must be float32 [n_q_heads]")
+
+
+_GENERIC_MASKED_ARGS = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
+                        c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                        c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+
+
 def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int,
                       n_q_heads: int, n_kv_heads: int, head_dim: int, softcap: float = 0.0,
-                      slopes: Optional[torch.Tensor] = None):
+                      slopes: Optional[torch.Tensor] = None, chunk: int = 0,
+                      log_bias: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, sinks: Optional[torch.Tensor] = None,
+                      gate: Optional[torch.Tensor] = None):
     """out[t] = softmax(scale q[t] K^T) V over the keys lo..positions[t] of token t's request, read from pages.
     q, out: [n, n_q_heads * head_dim] (last dimension contiguous); window <= 0 means all keys; softcap > 0 caps the
     scaled scores smoothly, softcap * tanh(score / softcap); slopes (float32 [n_q_heads]) adds
-    slopes[head] * (key position - query position) to the scaled scores."""
+    slopes[head] * (key position - query position) to the scaled scores.  chunk > 0: a query at position p sees the keys
+    p - p % chunk .. p only.  log_bias (r1, r2), float32 [n_q_heads] each: r1 * log(1 + r2 * distance) is taken off the
+    scaled scores.  sinks (float32 [n_q_heads]): exp(sink) is one more term of the softmax's denominator.  gate ([n,
+    n_q_heads] view of q's dtype): head h's output is multiplied by sigmoid(gate[t, h])."""
     n = q.shape[0]
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
         raise KernelError("attention: q and out must be [n, heads * head_dim] with a contiguous last dimension")
     if cache.dtype != q.dtype or out.dtype != q.dtype or not cache.is_contiguous() or \
             tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
         raise KernelError(f"attention: cache of shape {tuple(cache.shape)} / {cache.dtype} does not match the heads")
-    if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (n_q_heads,) or not slopes.is_contiguous()):
-        raise KernelError("attention: slopes must be float32 [n_q_heads]")
-    f = _func("attention_generic.cu", "lmsf_attention_generic_scores",
-              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
-               c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _per_head(slopes, n_q_heads, "slopes")
+    _per_head(sinks, n_q_heads, "sinks")
+    r1, r2 = log_bias if log_bias is not None else (None, None)
+    _per_head(r1, n_q_heads, "the logarithmic bias")
+    _per_head(r2, n_q_heads, "the logarithmic bias")
+    if gate is not None and (gate.shape != (n, n_q_heads) or gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise KernelError("attention: the gate must be [n, heads] of q's dtype")
+    f = _func("attention_generic.cu", "lmsf_attention_generic_masked", _GENERIC_MASKED_ARGS)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0),
            _i32(block_table, "block_table"), block_table.shape[1], block_size, _i32(token_seq, "token_seq"),
            _i32(positions, "positions"), float(scale), float(softcap or 0.0), _ptr(slopes), int(window or 0), n, n_q_heads,
-           n_kv_heads, head_dim, dtype_code(q.dtype), _stream())
+           n_kv_heads, head_dim, dtype_code(q.dtype), 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
+           int(chunk or 0), _ptr(r1), _ptr(r2), _ptr(sinks), _stream())
     _check(rc, "attention_generic.cu", "lmsf_attention_generic")
 
 
@@ -812,6 +835,40 @@ def stream_norm(res: torch.Tensor, y: Optional[torch.Tensor] = None, w_post: Opt
     _check(rc, "stream_norm.cu", "lmsf_stream_norm")
 
 
+def gated_branches(res: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor], y1: torch.Tensor,
+                   y2: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
+                   eps_next: float = 0.0):
+    """res += sigmoid(z[:, :D] + bias[:D]) * y1 + sigmoid(z[:, D:] + bias[D:]) * y2 (y2 may be None), then h = norm(res) *
+    w_next if h is given; one kernel, float32 inside.  res: float32 [n, D]; z: float32 [n, D or 2 D] (last dimension
+    contiguous); bias: float32 of z's width; y1, y2, h: contiguous [n, D] of the activation type."""
+    n, hidden = res.shape
+    width = (2 if y2 is not None else 1) * hidden
+    if res.dtype != torch.float32 or not res.is_contiguous():
+        raise KernelError("gated_branches: the residual stream must be contiguous float32")
+    if z.dtype != torch.float32 or z.shape != (n, width) or z.stride(1) != 1:
+        raise KernelError(f"gated_branches: the gate logits must be float32 [n, {width}]")
+    for name, t in (("y1", y1), ("y2", y2), ("h", h)):
+        if t is not None and (t.shape != res.shape or not t.is_contiguous() or t.dtype != y1.dtype):
+            raise KernelError(f"gated_branches: {name} must be contiguous, of the stream's shape and of one activation type")
+    f = _func("stream_norm.cu", "lmsf_gated_branches",
+              [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+               c_void_p])
+    rc = f(_ptr(res), _ptr(z), z.stride(0), _f32vec(bias, width, "bias"), _ptr(y1), _ptr(y2), _ptr(h),
+           _f32vec(w_next, hidden, "w_next"), n, hidden, float(eps_next), dtype_code(y1.dtype), _stream())
+    _check(rc, "stream_norm.cu", "lmsf_stream_norm")
+
+
+def stream_concat(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor):
+    """out = [a | b] in out's type: two float32 streams [n, D] side by side, [n, 2 D]."""
+    n, hidden = a.shape
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != a.shape or out.shape != (n, 2 * hidden) or \
+            not (a.is_contiguous() and b.is_contiguous() and out.is_contiguous()):
+        raise KernelError("stream_concat: two contiguous float32 streams [n, D] and out [n, 2 D]")
+    f = _func("stream_norm.cu", "lmsf_stream_concat", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(a), _ptr(b), n, hidden, dtype_code(out.dtype), _stream())
+    _check(rc, "stream_norm.cu", "lmsf_stream_norm")
+
+
 def stream_begin(res: torch.Tensor, x: torch.Tensor):
     """res = float(x): an embedding's output becomes the float32 residual stream."""
     if res.dtype != torch.float32 or res.shape != x.shape or not (res.is_contiguous() and x.is_contiguous()):
@@ -1023,6 +1080,47 @@ def latent_norm_cache_write(x: torch.Tensor, w: torch.Tensor, eps: float, cache:
     _check(rc, "latent_cache.cu", "lmsf_latent_cache")
 
 
+def latent_norm_rope_cache_write(x: torch.Tensor, w: torch.Tensor, eps: float, cache: torch.Tensor, positions: torch.Tensor,
+                                 token_seq: torch.Tensor, block_table: torch.Tensor, block_size: int, rank: int, rot_dim: int,
+                                 rot_n: int, inv_freq: Optional[torch.Tensor], error_flag: Optional[torch.Tensor] = None):
+    """cache[page of token t][slot] = [norm(x[t, :rank]) * w | key part | zeros]: the key part x[t, rank:rank + rot_dim] has
+    its first rot_n values rotated by the token's position (value i pairs with value i + rot_n / 2; inv_freq float32
+    [rot_n / 2]).  x: [n, rank + rot_dim] view; cache: [pages, 1, 1, block_size, padded]."""
+    n = x.shape[0]
+    padded = cache.shape[-1]
+    if x.shape != (n, rank + rot_dim) or x.stride(1) != 1 or cache.dtype != x.dtype or not cache.is_contiguous() or \
+            tuple(cache.shape[1:]) != (1, 1, block_size, padded) or padded < rank + rot_dim:
+        raise KernelError(f"latent cache: x [n, {rank + rot_dim}] and a cache [pages, 1, 1, {block_size}, >= {rank + rot_dim}] of one dtype")
+    if rot_n and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_n // 2 or not inv_freq.is_contiguous()):
+        raise KernelError("latent cache: inv_freq must hold rot_n / 2 float32 values")
+    f = _func("latent_cache.cu", "lmsf_latent_norm_rope_cache_write",
+              [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+               c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(x), x.stride(0), _f32vec(w, rank, "w"), _ptr(cache), cache.stride(0), _i32(positions, "positions"),
+           _i32(token_seq, "token_seq"), _i32(block_table, "block_table"), block_table.shape[1], block_size, n, rank, padded,
+           float(eps), int(rot_dim), int(rot_n), _ptr(inv_freq), dtype_code(x.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "latent_cache.cu", "lmsf_latent_cache")
+
+
+def latent_query_rope(qa: torch.Tensor, q: torch.Tensor, positions: torch.Tensor, heads: int, plain: int, rot_dim: int,
+                      rot_n: int, inv_freq: Optional[torch.Tensor], rank: int, padded: int):
+    """qa[t, h, rank:rank + rot_dim] = the rotated part q[t, h, plain:plain + rot_dim] of every head, its first rot_n values
+    rotated by the token's position; qa[t, h, rank + rot_dim:padded] = 0.  q: [n, heads * (plain + rot_dim)] view,
+    qa: [n, heads * padded]."""
+    n = q.shape[0]
+    if q.shape != (n, heads * (plain + rot_dim)) or q.stride(1) != 1 or qa.shape != (n, heads * padded) or qa.stride(1) != 1 \
+            or qa.dtype != q.dtype:
+        raise KernelError("latent query: q [n, heads * (plain + rot_dim)] and qa [n, heads * padded] of one dtype")
+    if rot_n and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_n // 2 or not inv_freq.is_contiguous()):
+        raise KernelError("latent query: inv_freq must hold rot_n / 2 float32 values")
+    f = _func("latent_cache.cu", "lmsf_latent_query_rope",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+               c_int, c_void_p])
+    rc = f(_ptr(q), q.stride(0), _ptr(qa), qa.stride(0), _i32(positions, "positions"), n, heads, plain, rot_dim, int(rot_n),
+           _ptr(inv_freq), rank, padded, dtype_code(q.dtype), _stream())
+    _check(rc, "latent_cache.cu", "lmsf_latent_cache")
+
+
 def head_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, head_dim: int):
     """x[t, h, :] *= sigmoid(gate[t, h]) in place.  x: [n, heads * head_dim], gate: [n, heads] (views, last dimension contiguous)."""
     n = x.shape[0]
@@ -1035,10 +1133,11 @@ def head_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, head_dim: int):
 
 def attention_shared_kv(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, block_size: int,
                         token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int, n_q_heads: int,
-                        head_dim: int, gate: Optional[torch.Tensor] = None):
+                        head_dim: int, gate: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None):
     """Attention of n_q_heads query heads over ONE cached vector per token that is key and value at once
     (cache [pages, 1, 1, block_size, head_dim]); out[t, h] = sigmoid(gate[t, h]) * softmax(scale q K^T) K when a gate
-    ([n, n_q_heads] view) is given.  The plain kernel: any mix of tokens, fixed summation order."""
+    ([n, n_q_heads] view) is given; sinks (float32 [n_q_heads]): exp(sink) is one more term of the softmax's denominator.
+    The plain kernel: any mix of tokens, fixed summation order."""
     n = q.shape[0]
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
         raise KernelError("attention: q and out must be [n, heads * head_dim] with a contiguous last dimension")
@@ -1047,14 +1146,13 @@ def attention_shared_kv(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor,
         raise KernelError(f"attention: cache of shape {tuple(cache.shape)} / {cache.dtype} is not [pages, 1, 1, {block_size}, {head_dim}]")
     if gate is not None and (gate.shape != (n, n_q_heads) or gate.stride(1) != 1 or gate.dtype != q.dtype):
         raise KernelError("attention: the gate must be [n, heads] of q's dtype")
-    f = _func("attention_generic.cu", "lmsf_attention_generic_ext",
-              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
-               c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
-               c_void_p])
+    _per_head(sinks, n_q_heads, "sinks")
+    f = _func("attention_generic.cu", "lmsf_attention_generic_masked", _GENERIC_MASKED_ARGS)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0),
            _i32(block_table, "block_table"), block_table.shape[1], block_size, _i32(token_seq, "token_seq"),
            _i32(positions, "positions"), float(scale), 0.0, None, int(window or 0), n, n_q_heads, 1, head_dim,
-           dtype_code(q.dtype), 1, _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+           dtype_code(q.dtype), 1, _ptr(gate), gate.stride(0) if gate is not None else 0, 0, None, None, _ptr(sinks),
+           _stream())
     _check(rc, "attention_generic.cu", "lmsf_attention_generic")
 
 
@@ -1187,6 +1285,24 @@ def moe_combine(out: torch.Tensor, down: torch.Tensor, pair_row: torch.Tensor, w
               [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
     rc = f(_ptr(out), _ptr(down), _i32(pair_row, "pair_row"), _ptr(wts), top, _ptr(shared), _ptr(gate),
            gate.stride(0) if gate is not None else 0, n, width, dtype_code(out.dtype), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")
+
+
+GLU_ACTS = {"silu": 0, "swish": 0, "gelu_tanh": 1}
+
+
+def moe_weighted_glu(out: torch.Tensor, y: torch.Tensor, pair_row: torch.Tensor, wts: Optional[torch.Tensor], act: str = "silu"):
+    """out[r] = act(w y[r, :F]) * (w y[r, F:]) for the row r = pair_row[pair] of every (token, choice) pair and its routing
+    weight w = wts[pair] (None: 1): gated experts whose weight multiplies what the expert reads.  y: [pairs, 2 F]."""
+    pairs, F = out.shape
+    if y.shape != (pairs, 2 * F) or not (y.is_contiguous() and out.is_contiguous()) or y.dtype != out.dtype:
+        raise KernelError("moe: y must be contiguous [pairs, 2 F] and out [pairs, F] of one dtype")
+    if pair_row.numel() != pairs or (wts is not None and (wts.dtype != torch.float32 or wts.numel() != pairs or not wts.is_contiguous())):
+        raise KernelError("moe: one row and one float32 weight per pair")
+    if act not in GLU_ACTS:
+        raise KernelError(f"moe: unknown gated activation {act!r} (known: {', '.join(sorted(GLU_ACTS))})")
+    f = _func("moe.cu", "lmsf_moe_weighted_glu", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(y), _i32(pair_row, "pair_row"), _ptr(wts), pairs, F, GLU_ACTS[act], dtype_code(out.dtype), _stream())
     _check(rc, "moe.cu", "lmsf_moe")
 
 

@@ -37,7 +37,9 @@ class PagedAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding] = None, window: Optional[int] = None,
                  scale: Optional[float] = None, bias: bool = False, softcap: Optional[float] = None,
-                 value_dim: Optional[int] = None, qk_norm: bool = False, qk_norm_eps: float = 1e-6):
+                 value_dim: Optional[int] = None, qk_norm: bool = False, qk_norm_eps: float = 1e-6,
+                 qk_norm_weights: bool = True, value_norm: bool = False, chunk: Optional[int] = None,
+                 head_gate: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads cannot be grouped over {num_kv_heads} kv heads")
         # head_dim is the stored size of a query or key head, value_dim that of a value head (default: the same).  The
@@ -54,6 +56,19 @@ class PagedAttention(Mixer):
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         # RMS norm of every query and key head before the rotation (weights q_norm, k_norm [qk_dim], shared by the heads)
         self.qk_norm, self.qk_norm_eps = bool(qk_norm), float(qk_norm_eps)
+        # qk_norm_weights False: the norm has no weight (a division by the root mean square alone).  value_norm: every value
+        # head is divided by its root mean square over value_dim on its way into the cache (no weight either)
+        self.qk_norm_weights, self.value_norm = bool(qk_norm_weights), bool(value_norm)
+        if self.value_norm and not self.qk_norm:
+            raise ValueError("a norm of the values goes with a norm of queries and keys")
+        # chunk c: a query at position p sees the keys of its own chunk of positions, p - p % c .. p, counted from the
+        # request's first token.  Pages of earlier chunks are kept (a request may be cut anywhere)
+        self.chunk = int(chunk) if chunk else None
+        # head_gate: head h's output is multiplied by sigmoid(w_h . x), one number per token and head, before the output
+        # projection; the rows w_h are stored behind q, k and v in the merged matrix
+        self.head_gate = bool(head_gate)
+        if self.head_gate and bias:
+            raise ValueError("a gate per head with projection biases is not built")
         self.q_norm: Optional[torch.Tensor] = None
         self.k_norm: Optional[torch.Tensor] = None
         self._qn32: Optional[torch.Tensor] = None
@@ -74,12 +89,12 @@ class PagedAttention(Mixer):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         H, G, dk, dv, D = self.num_heads, self.num_kv_heads, self.qk_dim, self.value_dim, self.hidden_size
-        specs = {"qkv": WeightSpec([(H * dk, D), (G * dk, D), (G * dv, D)]),
+        specs = {"qkv": WeightSpec([(H * dk, D), (G * dk, D), (G * dv, D)] + ([(H, D)] if self.head_gate else [])),
                  "o": WeightSpec([(D, H * dv)])}
         if self.has_bias:
             specs["qkv_bias"] = WeightSpec([(H * dk,), (G * dk,), (G * dv,)])
             specs["o_bias"] = WeightSpec([(D,)])
-        if self.qk_norm:
+        if self.qk_norm and self.qk_norm_weights:
             specs["q_norm"] = WeightSpec([(dk,)], keep_fp32=True)
             specs["k_norm"] = WeightSpec([(dk,)], keep_fp32=True)
         return specs
@@ -98,8 +113,9 @@ class PagedAttention(Mixer):
             for name in ("qkv", "qkv_bias"):
                 if name in tensors:
                     t = tensors[name]
-                    q, k, v = t[:H * dk], t[H * dk:(H + G) * dk], t[(H + G) * dk:]
-                    tensors[name] = torch.cat([pad_heads(q, H, dk), pad_heads(k, G, dk), pad_heads(v, G, dv)], 0).contiguous()
+                    q, k, v = t[:H * dk], t[H * dk:(H + G) * dk], t[(H + G) * dk:(H + G) * dk + G * dv]
+                    rest = t[(H + G) * dk + G * dv:]            # the rows of a gate per head, if any
+                    tensors[name] = torch.cat([pad_heads(q, H, dk), pad_heads(k, G, dk), pad_heads(v, G, dv), rest], 0).contiguous()
             if "o" in tensors:
                 o = tensors["o"].reshape(-1, H, dv)
                 po = o.new_zeros((o.shape[0], H, hd))
@@ -116,14 +132,14 @@ class PagedAttention(Mixer):
     def prepare(self, dtype, device) -> None:
         if self.position_encoding is not None:
             self.position_encoding.prepare(dtype, device)
-        if self.qk_norm:
+        if self.qk_norm and self.qk_norm_weights:
             self._qn32, self._kn32 = self.q_norm.float().contiguous(), self.k_norm.float().contiguous()
         if dtype == torch.bfloat16 and not kernels.mma_attention_supported(dtype, self.head_dim):
             # right but slow: said once, so that nobody wonders where the time goes
             warnings.warn(f"head_dim {self.head_dim} is beyond the tensor-core attention kernels "
                           f"(up to {kernels.MMA_MAX_HEAD_DIM}); bfloat16 attention runs on the generic kernel",
                           RuntimeWarning, stacklevel=2)
-        elif dtype == torch.bfloat16 and (self.softcap or self._slopes() is not None):
+        elif dtype == torch.bfloat16 and (self.softcap or self._slopes() is not None) and not self._masked_fast():
             warnings.warn("a cap on the attention scores, or a bias on them, is taken by the generic kernel only; "
                           "bfloat16 attention runs on it", RuntimeWarning, stacklevel=2)
         slopes = self._slopes()
@@ -132,6 +148,13 @@ class PagedAttention(Mixer):
 
     def _slopes(self) -> Optional[torch.Tensor]:
         return self.position_encoding.score_slopes() if self.position_encoding is not None else None
+
+    def _log_bias(self):
+        f = getattr(self.position_encoding, "score_log_bias", None)
+        return f() if f is not None else None
+
+    def _masked_fast(self) -> bool:
+        return False
 
     def forward(self, ctx: StepContext, h, cache: LayerCache, then: Optional[NormAfter] = None):
         group = ctx.groups[cache.group]
@@ -150,17 +173,22 @@ class PagedAttention(Mixer):
             out = torch.empty((ctx.n_tokens, self.q_size), dtype=hx.dtype, device=hx.device)
             self.attend(ctx, out, q, cache.kv, group)
             return self._project_out(out, then)
+        gate = None
         if cache.owner:
             qkv = matmul_tn(h, self.qkv, bias=self.qkv_bias)
             q = qkv[:, :self.q_size]
             k = qkv[:, self.q_size:self.q_size + self.kv_size]
-            v = qkv[:, self.q_size + self.kv_size:]
+            v = qkv[:, self.q_size + self.kv_size:self.q_size + 2 * self.kv_size]
+            if self.head_gate:
+                gate = qkv[:, self.q_size + 2 * self.kv_size:]
         else:  # keys and values are another call's: only the queries are needed
             q = matmul_tn(h, self.qkv[:self.q_size], bias=None if self.qkv_bias is None else self.qkv_bias[:self.q_size])
             k = v = None
-        if self.position_encoding is not None and fused is None:
+            if self.head_gate:
+                gate = matmul_tn(h, self.qkv[self.q_size + 2 * self.kv_size:])
+        if self.position_encoding is not None and fused is None and self._slopes() is None and self._log_bias() is None:
             if self.qk_norm:
-                raise ValueError("a norm of queries and keys goes with a rotary encoding or none")
+                raise ValueError("a norm of queries and keys goes with a rotary encoding, a bias on the scores or none")
             self.position_encoding.apply(ctx, q, k, self.num_heads, self.num_kv_heads, self.head_dim)
         inv_freq, rot_dim, is_neox = fused if fused is not None else (None, 0, True)
         if self.qk_norm:
@@ -168,13 +196,14 @@ class PagedAttention(Mixer):
             kernels.qk_norm_rope_cache_write(q, k, v, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
                                              cache.kv if cache.owner else None, inv_freq, rot_dim, is_neox, self.num_heads,
                                              self.num_kv_heads, self.head_dim, self.qk_dim, self._qn32, self._kn32,
-                                             self.qk_norm_eps, ctx.error_flag)
+                                             self.qk_norm_eps, ctx.error_flag, weightless=not self.qk_norm_weights,
+                                             v_norm_dim=self.value_dim if self.value_norm else 0)
         elif fused is not None or cache.owner:
             kernels.rope_cache_write(q, k, v, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
                                      cache.kv if cache.owner else None, inv_freq, rot_dim, is_neox, self.num_heads,
                                      self.num_kv_heads, self.head_dim, ctx.error_flag)
         out = torch.empty((ctx.n_tokens, self.q_size), dtype=q.dtype, device=q.device)
-        self.attend(ctx, out, q, cache.kv, group)
+        self.attend(ctx, out, q, cache.kv, group, gate)
         return self._project_out(out, then)
 
     def _project_out(self, out: torch.Tensor, then: Optional[NormAfter]):
@@ -184,21 +213,25 @@ class PagedAttention(Mixer):
                 return p
         return matmul_tn(out, self.o, bias=self.o_bias)
 
-    def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group) -> None:
+    def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, gate=None) -> None:
         paged_attend(ctx, out, q, kv, group, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                     scale=self.scale, window=self.window, softcap=self.softcap, slopes=self._slopes())
+                     scale=self.scale, window=self.window, softcap=self.softcap, slopes=self._slopes(), chunk=self.chunk,
+                     log_bias=self._log_bias(), gate=gate)
 
 
 def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, *, num_heads: int,
                  num_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None, softcap: float = 0.0,
-                 slopes: Optional[torch.Tensor] = None, kv_planes: int = 2) -> None:
+                 slopes: Optional[torch.Tensor] = None, kv_planes: int = 2, chunk: Optional[int] = None,
+                 log_bias=None, gate: Optional[torch.Tensor] = None) -> None:
     """Attention over pages for any mix of tokens.  bfloat16 with a head size up to 128: single tokens go to the
     split-key decode kernel, longer portions to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for
     head sizes 64 and 128, mma.sync otherwise).  Everything else, float32 included, runs on the generic kernel, which is
     also their plain twin.  kv_planes 1: one cached vector per token and kv head is key and value at once (the fast
-    kernels only; the caller keeps its own plain kernel for that layout)."""
-    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and \
-            not ctx.extras.get("force_generic_attention"):
+    kernels only; the caller keeps its own plain kernel for that layout).  chunk: a query sees the keys of its own chunk of
+    positions only; log_bias (r1, r2): r1 * log(1 + r2 * distance) is taken off the scores (both: the generic kernel);
+    gate [n, heads]: the output of head h is multiplied by sigmoid(gate[:, h])."""
+    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and not chunk and \
+            log_bias is None and not ctx.extras.get("force_generic_attention"):
         if ctx.n_decode_seqs:
             max_ctx = ctx.extras.get("decode_max_ctx")
             if max_ctx is None:
@@ -263,9 +296,11 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
             kernels.attention_prefill(out, q, kv, group.block_table, group.block_size, ctx.q_tile_seq,
                                       ctx.q_tile_q0, ctx.n_q_tiles, ctx.cu_q, ctx.ctx_len, scale,
                                       window or 0, num_heads, num_kv_heads, head_dim, kv_planes=kv_planes)
+        if gate is not None:
+            kernels.head_gate_(out, gate, num_heads, head_dim)
         return
     if kv_planes != 2:
         raise ValueError("the plain attention kernel of keys and values takes a cache of two planes")
     kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
                               scale, window or 0, num_heads, num_kv_heads, head_dim,
-                              softcap=softcap, slopes=slopes)
+                              softcap=softcap, slopes=slopes, chunk=chunk or 0, log_bias=log_bias, gate=gate)

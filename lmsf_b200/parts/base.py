@@ -231,11 +231,12 @@ class Normed:
 
 
 class StreamEntry(Part):
-    """Changes the float32 residual stream in place before a call of the order: `forward(ctx, res, first, n_pass)`,
-    where `first` is the stream as the embedding left it."""
+    """Changes the float32 residual stream before a call of the order: `forward(ctx, res, first, n_pass)`, where `first`
+    is the stream as the embedding left it.  It works in place and returns None, or returns the tensor that is the
+    stream from here on."""
     needs_first = False     # True: the model keeps a copy of the embedding's output for it
 
-    def forward(self, ctx: "StepContext", res: torch.Tensor, first: Optional[torch.Tensor], n_pass: int) -> None:
+    def forward(self, ctx: "StepContext", res: torch.Tensor, first: Optional[torch.Tensor], n_pass: int) -> Optional[torch.Tensor]:
         raise NotImplementedError
 
 

@@ -171,3 +171,50 @@ class BranchNormBlock(Block):
         h = torch.empty(res.shape, dtype=ctx.dtype, device=res.device)
         kernels.stream_norm(res, h=h)
         return h
+
+
+@register_part("block", "parallel_gated")
+class ParallelGatedBlock(Block):
+    """One norm, two branches side by side, each behind a gate of its own:
+         h = norm(x);  x <- x + sigmoid(W1 h + b1) * mixer(h) + sigmoid(W2 h + b2) * ff(h)
+    The gates are vectors of the stream's width, multiplied element by element; their logits come from ONE product
+    (`gates`: a `gate_logits` part whose matrix stacks W1 and W2) in float32.  One kernel ends the layer: both sigmoids,
+    both products, the float32 sum into the stream and, when the next block starts with a norm of the same kind, that
+    norm too (`kernels.gated_branches`).  A layer may have no feed-forward (and then no second gate)."""
+    ROLES = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward", "gates": "linear"}
+    OPTIONAL_ROLES = ("feed_forward",)
+    fuses_next_norm = True
+
+    def __init__(self, parts: Dict[str, Part]):
+        super().__init__(parts)
+        self.norm, self._mixer, self.gates = parts["norm"], parts["mixer"], parts["gates"]
+        self.feed_forward = parts.get("feed_forward")
+        if not hasattr(self.norm, "weight_f32") or getattr(self.norm, "has_layer_scale", False):
+            raise ValueError("the parallel block takes a norm that is a factor per row times a weight (rmsnorm)")
+        branches = 2 if self.feed_forward is not None else 1
+        if not hasattr(self.gates, "logits") or self.gates.out_features != branches * self.norm.hidden_size:
+            raise ValueError(f"the parallel block needs gate logits of {branches} x the stream's width")
+
+    def entry(self) -> Optional[Tuple[Norm, Part]]:
+        return self.norm, self._mixer
+
+    def forward(self, ctx: StepContext, x, res: Optional[torch.Tensor], cache: LayerCache,
+                next_entry: Optional[Tuple[Norm, Part]] = None):
+        if x is not None and not isinstance(x, Normed) and res is None:      # the embedding's output starts the stream
+            if x.dtype == torch.float32:
+                res = x
+            else:
+                res = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+                kernels.stream_begin(res, x)
+            x = None
+        h, res = self.norm.forward_residual(x, res)       # x: None (a complete stream), a Normed, or a pending branch
+        z = self.gates.logits(h)
+        a = self._mixer.forward(ctx, h, cache)
+        f = self.feed_forward.forward(ctx, h) if self.feed_forward is not None else None
+        nxt = next_entry[0] if next_entry is not None and hasattr(next_entry[0], "weight_f32") and \
+            not getattr(next_entry[0], "has_layer_scale", False) else None
+        h_next = torch.empty_like(a) if nxt is not None else None
+        kernels.gated_branches(res, z, self.gates.bias_f32(), a, f, h=h_next,
+                               w_next=nxt.weight_f32() if nxt is not None else None,
+                               eps_next=nxt.eps if nxt is not None else 0.0)
+        return (Normed(h_next, nxt, res) if nxt is not None else None), res

@@ -90,7 +90,9 @@ class DecoderModel:
             if call.entry is not None:
                 if res is None or x is not None:
                     raise ValueError("a stream entry needs a block before it (or an embedding) that leaves nothing pending")
-                self.entries[call.entry].forward(ctx, res, first, call.entry_pass)
+                replaced = self.entries[call.entry].forward(ctx, res, first, call.entry_pass)
+                if replaced is not None:
+                    res = replaced
             # a block that can take the next block's first norm into its last product is told that norm and its reader
             # (not across an entry that changes the stream in between)
             entry = None

@@ -13,9 +13,12 @@ from .base import Part, StepContext, WeightSpec, register_part
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, as_stream: bool = False):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.scale = float(scale)      # every embedding is multiplied by it (1 for Llama; sqrt(width) elsewhere)
+        # as_stream: the embedding's output is handed over as the float32 residual stream (with a second copy for layers
+        # that read it again), for models whose first block or stream entry wants a complete stream
+        self.emits_stream = bool(as_stream)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -25,6 +28,20 @@ class TokenEmbedding(Part):
         x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=self.weight.dtype, device=self.weight.device)
         kernels.embedding(x, self.weight, ctx.token_ids, ctx.error_flag, scale=self.scale)
         return x
+
+    def forward_stream(self, ctx: StepContext, keep: bool = False):
+        """(stream, copy of it or None), both float32 [n_tokens, hidden]."""
+        x = self.forward(ctx)
+        if x.dtype == torch.float32:
+            res = x
+        else:
+            res = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            kernels.stream_begin(res, x)
+        first = None
+        if keep:
+            first = torch.empty_like(res)
+            kernels.stream_begin(first, x)
+        return res, first
 
 
 @register_part("embedding", "normed_token_embedding")

@@ -134,3 +134,40 @@ class Linear(Part):
                 raise ValueError("a scaled or capped output is float32 (out_dtype='float32')")
             kernels.scale_softcap_(y, self.out_scale, self.out_softcap)
         return y
+
+
+@register_part("linear", "gate_logits")
+class GateLogits(Part):
+    """The logits of one or several gates that read the same input: z = x W^T in float32, W the gates' matrices stacked
+    along the output dimension, and their biases (kept apart, in float32, for the kernel that applies the sigmoids)."""
+    graph_safe = True
+
+    def __init__(self, in_features: int, out_features: Union[int, Sequence[int]], bias: bool = True):
+        self.in_features = int(in_features)
+        self.out_splits: List[int] = [int(out_features)] if isinstance(out_features, int) else [int(o) for o in out_features]
+        self.out_features = sum(self.out_splits)
+        self.has_bias = bool(bias)
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self._bias32: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = {"weight": WeightSpec([(o, self.in_features) for o in self.out_splits])}
+        if self.has_bias:
+            specs["bias"] = WeightSpec([(o,) for o in self.out_splits], keep_fp32=True)
+        return specs
+
+    def prepare(self, dtype, device) -> None:
+        self._bias32 = self.bias.float().contiguous() if self.has_bias else None
+
+    def bias_f32(self) -> Optional[torch.Tensor]:
+        return self._bias32
+
+    def logits(self, x: torch.Tensor) -> torch.Tensor:
+        return matmul_tn(x, self.weight, out_dtype=torch.float32)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        z = self.logits(x)
+        if self._bias32 is not None:
+            kernels.bias_add(z, self._bias32)
+        return z

@@ -9,6 +9,11 @@ s + correction among the experts of the `group_keep` best of `groups` groups of 
 two largest s + correction) and weighs by the chosen s themselves; `activation="clamped_swiglu"` gives every expert a gate
 and an up matrix: g = min(gate h, limit), u = clamp(up h, -limit, limit), expert(h) = (g sigmoid(alpha g) (u + 1)) Wdown^T.
 
+`routing="sigmoid_top"` is the same scoring without groups or correction.  `activation="silu"` or `"gelu_tanh"` gives gated
+experts without the clamp, expert(h) = (act(gate h) * (up h)) Wdown^T; with `weight_on_input` the routing weight multiplies
+what the expert reads, out = sum_j expert_(e_j)(w_j h): gate and up are linear in h, so the weight is applied, in float32, to
+their products inside the activation kernel, and the combine adds the experts' outputs unweighted.
+
 All experts' matrices are stacked ([experts, ff, width], [experts, width, ff]).  The routing is sorted on the device
 (csrc/moe.cu): no value comes back to the host, and a step's launches have the same shape whatever the routing is, so
 decode steps can be replayed from CUDA graphs.  The router and the shared expert's gate are rows of one float32 product.
@@ -34,22 +39,28 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_size: int, shared_size: int = 0,
                  activation: str = "relu2", router_bias: bool = True, shared_gate: bool = True,
                  routing: str = "softmax_top", groups: int = 1, group_keep: int = 1, limit: Optional[float] = None,
-                 alpha: float = 1.702):
+                 alpha: float = 1.702, weight_on_input: bool = False):
         if not (0 < top_k <= num_experts):
             raise ValueError(f"{top_k} choices of {num_experts} experts")
-        if activation not in kernels.MOE_ACTS and activation != "clamped_swiglu":
-            raise ValueError(f"activation {activation!r} is not supported (known: relu2, clamped_swiglu, none)")
-        if routing not in ("softmax_top", "sigmoid_groups"):
-            raise ValueError(f"routing {routing!r} is not supported (known: softmax_top, sigmoid_groups)")
+        if activation not in kernels.MOE_ACTS and activation != "clamped_swiglu" and activation not in kernels.GLU_ACTS:
+            raise ValueError(f"activation {activation!r} is not supported (known: relu2, clamped_swiglu, silu, gelu_tanh, none)")
+        if routing not in ("softmax_top", "sigmoid_groups", "sigmoid_top"):
+            raise ValueError(f"routing {routing!r} is not supported (known: softmax_top, sigmoid_groups, sigmoid_top)")
+        if routing == "sigmoid_top":
+            routing, groups, group_keep = "sigmoid_groups", 1, 1
         self.routing, self.groups, self.group_keep = routing, int(groups), int(group_keep)
         if routing == "sigmoid_groups" and (self.groups < 1 or num_experts % self.groups or not (1 <= self.group_keep <= self.groups)
                                             or self.group_keep * (num_experts // self.groups) < top_k):
             raise ValueError(f"{num_experts} experts in {groups} groups of which {group_keep} are kept cannot give {top_k} choices")
-        self.gated = activation == "clamped_swiglu"        # experts with a gate and an up matrix
-        if self.gated and not (limit is not None and limit > 0):
+        self.clamped = activation == "clamped_swiglu"
+        self.gated = self.clamped or activation in kernels.GLU_ACTS        # experts with a gate and an up matrix
+        self.weight_on_input = bool(weight_on_input)
+        if self.weight_on_input and (self.clamped or not self.gated):
+            raise ValueError("the routing weight on the expert's input is built for silu and gelu_tanh gated experts")
+        if self.clamped and not (limit is not None and limit > 0):
             raise ValueError("the clamped activation needs a positive limit")
         if self.gated and shared_size:
-            raise ValueError("a shared expert with the clamped activation is not built")
+            raise ValueError("a shared expert beside gated experts is not built")
         self.limit, self.alpha = (float(limit) if limit is not None else None), float(alpha)
         self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.expert_size, self.shared_size = int(expert_size), int(shared_size or 0)
@@ -63,6 +74,7 @@ class RoutedExperts(FeedForward):
         self.shared_up: Optional[torch.Tensor] = None
         self.shared_down: Optional[torch.Tensor] = None
         self._bias32: Optional[torch.Tensor] = None
+        self._one_weights: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, E, F = self.hidden_size, self.num_experts, self.expert_size
@@ -81,6 +93,13 @@ class RoutedExperts(FeedForward):
 
     def prepare(self, dtype, device) -> None:
         self._bias32 = self.router_bias.float().contiguous() if self.has_router_bias else None
+        self._one_weights = torch.ones(64 * self.top_k, dtype=torch.float32, device=device) if self.weight_on_input else None
+
+    def _ones(self, n: int, k: int, device) -> torch.Tensor:
+        if self._one_weights is None or self._one_weights.numel() < n * k:      # grows outside a graph's capture only
+            self._one_weights = torch.ones(max(n * k, 2 * (self._one_weights.numel() if self._one_weights is not None else 0)),
+                                           dtype=torch.float32, device=device)
+        return self._one_weights[:n * k].view(n, k)
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         n, D, E, K, F = h.shape[0], self.hidden_size, self.num_experts, self.top_k, self.expert_size
@@ -116,7 +135,10 @@ class RoutedExperts(FeedForward):
             kernels.moe_grouped(y, h, up3, row_token, tiles, meta, act=act)
         if self.gated:                                      # [pairs, gate | up] -> [pairs, F]
             y2 = torch.empty((pairs, F), dtype=h.dtype, device=dev)
-            kernels.clamped_glu(y2, y, self.limit, self.alpha)
+            if self.clamped:
+                kernels.clamped_glu(y2, y, self.limit, self.alpha)
+            else:
+                kernels.moe_weighted_glu(y2, y, pair_row, wts if self.weight_on_input else None, self.activation)
             y = y2
         if use_tc:
             kernels.moe_grouped_tc(d, y, down3, None, tiles, meta, error_flag=flag)
@@ -129,5 +151,7 @@ class RoutedExperts(FeedForward):
                 kernels.relu2_(s)
             shared = matmul_tn(s, self.shared_down)
         out = torch.empty((n, D), dtype=h.dtype, device=dev)
+        if self.weight_on_input:
+            wts = self._ones(n, K, dev)                     # the weights are inside the experts already
         kernels.moe_combine(out, d, pair_row, wts, shared, z[:, E] if self.has_shared_gate else None)
         return out

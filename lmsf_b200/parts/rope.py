@@ -15,7 +15,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from .. import kernels
-from .base import PositionEncoding, StepContext, register_part
+from .base import PositionEncoding, StepContext, WeightSpec, register_part
 
 
 def rope_inverse_frequencies(rot_dim: int, theta: float, scaling_type: str = "default", factor: float = 1.0,
@@ -110,3 +110,28 @@ class DistanceBias(PositionEncoding):
 
     def score_slopes(self) -> Optional[torch.Tensor]:
         return self.slopes
+
+
+@register_part("position_encoding", "log_distance_bias")
+class LogDistanceBias(PositionEncoding):
+    """Positions enter the scores, not q and k: r1[head] * log(1 + r2[head] * (query position - key position)) is taken
+    off every scaled score.  r1 and r2 are learned, one number each per query head (weights `r1`, `r2`)."""
+    graph_safe = True
+
+    def __init__(self, num_heads: int):
+        self.num_heads = int(num_heads)
+        self.r1: Optional[torch.Tensor] = None
+        self.r2: Optional[torch.Tensor] = None
+        self._r: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+
+    def weight_specs(self):
+        return {"r1": WeightSpec([(self.num_heads,)], keep_fp32=True), "r2": WeightSpec([(self.num_heads,)], keep_fp32=True)}
+
+    def prepare(self, dtype, device) -> None:
+        self._r = (self.r1.float().contiguous(), self.r2.float().contiguous())
+
+    def apply(self, ctx, q, k, n_q_heads, n_kv_heads, head_dim) -> None:
+        return None
+
+    def score_log_bias(self) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        return self._r
