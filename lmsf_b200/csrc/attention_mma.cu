@@ -25,14 +25,15 @@ namespace lmsf {
 namespace fa {
 
 constexpr int HD = LMSF_HEAD_DIM;
-static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 between 16 and 128");
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 between 16 and 256");
 // stages of 64 keys in flight per block
 #ifdef LMSF_KV_STAGES
 constexpr int kStages = LMSF_KV_STAGES;
 #else
 // head size 64: three stages of 16 KB leave room for four blocks on an SM, so that 64 requests x 8 kv heads run in
 // one wave (with four stages and three blocks per SM they took 72 us a layer in two waves)
-constexpr int kStages = HD < 64 ? 4 : 3;
+// head sizes beyond 208: two stages, so that the ring with one stage more still fits an SM's shared memory
+constexpr int kStages = HD < 64 ? 4 : (HD > 208 ? 2 : 3);
 #endif
 constexpr int kKSteps = HD / 16;   // k-steps of q k^T; also pairs of 8-wide output tiles of p v
 constexpr float kLog2e = 1.4426950408889634f;
@@ -61,6 +62,7 @@ struct DecodeArgs {
   // Splits per request instead of one number for all: blockIdx.x is an entry of this list, {request, split, splits of
   // the request, splits of the requests before it}; a request of -1 is padding.  Null: every request has n_splits.
   const int4* items;
+  ScoreExtras x;
 };
 
 // Online-softmax state of the two rows (lane / 4 and lane / 4 + 8) that a thread holds.
@@ -115,11 +117,19 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   for (int i = threadIdx.x; i < n_head; i += kDecThreads) s_table[i] = table[i];
   const int token = a.cu_q[seq];
   const int ctx = a.ctx_len[seq];
-  const int lo = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int lo = first_seen(ctx - 1, a.window, a.x.chunk);     // the new token sits at position ctx - 1
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g4 = lane >> 2, t4 = lane & 3;
   const int head0 = kvh * a.group + hchunk * 16;               // first query head of this block
   const int n_heads = min(16, a.group - hchunk * 16);          // valid rows
+  // the constants of this thread's two rows (heads); they are weights, which no kernel of the step writes
+  const bool biased = a.x.r1 != nullptr;
+  float r1[2] = {0.f, 0.f}, r2[2] = {0.f, 0.f};
+  if (biased) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      if (g4 + h * 8 < n_heads) { r1[h] = a.x.r1[head0 + g4 + h * 8]; r2[h] = a.x.r2[head0 + g4 + h * 8]; }
+  }
 
   // tiles of 64 keys aligned to absolute positions; this split's share of them
   const int tile_lo = lo / kDecTile, tile_hi = (ctx + kDecTile - 1) / kDecTile;
@@ -208,7 +218,9 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + j * 8 + t4 * 2 + (e & 1);
-        const float v = (key >= lo && key < ctx) ? s[j][e] * sl2 : -INFINITY;
+        const bool ok = key >= lo && key < ctx;
+        float v = ok ? s[j][e] * sl2 : -INFINITY;
+        if (biased && ok) v -= log_distance_bias2(r1[e >> 1], r2[e >> 1], ctx - 1 - key);
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -297,6 +309,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     }
     const int head = head0 + row;
     if (n_splits == 1) {
+      if (a.x.sinks) L += exp2f(a.x.sinks[head] * kLog2e - M);   // M is finite: the new token's own key is seen
       a.out[(size_t)token * a.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
     } else if (a.cluster) {
       st_cluster_f32(sm_part + split * kPS + row * HD + d, 0, L > 0.f ? acc / L : 0.f);
@@ -314,9 +327,11 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     if (split != 0) return;
     for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
       const int row = idx / HD, d = idx % HD;
-      float M = -INFINITY;
+      // a sink joins as one more part whose log-sum-exp is the sink itself and whose output is zero
+      const float sink2 = a.x.sinks ? a.x.sinks[head0 + row] * kLog2e : -INFINITY;
+      float M = sink2;
       for (int s = 0; s < n_splits; ++s) M = fmaxf(M, sm_part[s * kPS + R * HD + row]);
-      float acc = 0.f, L = 0.f;
+      float acc = 0.f, L = sink2 == -INFINITY ? 0.f : exp2f(sink2 - M);
       for (int s = 0; s < n_splits; ++s) {
         const float lse = sm_part[s * kPS + R * HD + row];
         const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
@@ -350,7 +365,8 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     __syncthreads();
     for (int row = warp; row < n_heads; row += kDecWarps) {
       float* w = s_w + row * n_splits;
-      float M = -INFINITY;
+      const float sink2 = a.x.sinks ? a.x.sinks[head0 + row] * kLog2e : -INFINITY;
+      float M = sink2;
       for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, w[s]);
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
@@ -362,6 +378,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
       }
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+      if (sink2 != -INFINITY) L += exp2f(sink2 - M);
       const float inv = 1.0f / L;
       for (int s = lane; s < n_splits; s += 32) w[s] *= inv;
     }
@@ -387,9 +404,10 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   for (int idx = threadIdx.x; idx < n_heads * HD; idx += kDecThreads) {
     const int row = idx / HD, d = idx % HD;
     const size_t base = base0 + (size_t)row * n_splits;
-    float M = -INFINITY;
+    const float sink2 = a.x.sinks ? a.x.sinks[head0 + row] * kLog2e : -INFINITY;
+    float M = sink2;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(a.part_lse + base + s));
-    float acc = 0.f, L = 0.f;
+    float acc = 0.f, L = sink2 == -INFINITY ? 0.f : exp2f(sink2 - M);
     for (int s = 0; s < n_splits; ++s) {
       const float lse = __ldcg(a.part_lse + base + s);
       const float f = lse == -INFINITY ? 0.f : exp2f(lse - M);
@@ -410,13 +428,14 @@ struct ItemArgs {
   const int* ctx_len; const int* seq_ids; int n_served; int window;
   int blocks_per_split, slots, capacity;
   int4* items;
+  int chunk;
 };
 __global__ void __launch_bounds__(32) decode_items_kernel(ItemArgs a) {
   const int lane = threadIdx.x;
   auto keys_of = [&](int i) {
     const int seq = a.seq_ids ? a.seq_ids[i] : i;
     const int ctx = a.ctx_len[seq];
-    return max(1, a.window > 0 ? min(ctx, a.window) : ctx);
+    return max(1, ctx - first_seen(ctx - 1, a.window, a.chunk));
   };
   auto warp_sum = [&](long long v) {
 #pragma unroll
@@ -585,7 +604,8 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
                                          const int* block_table, int max_blocks, const int* seq_ids, int n_served,
                                          int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
                                          int n_q_heads, int head_dim, int n_splits, int block_warps, void* scratch,
-                                         int kv_planes, void* stream) {
+                                         int kv_planes, int chunk, const float* r1, const float* r2, const float* sinks,
+                                         void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (n_served <= 0) return 0;
@@ -613,6 +633,8 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
     LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
+  if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0) LMSF_REFUSE("attention_decode: the distance bias takes both constants; chunk >= 0");
+  a.x = ScoreExtras{chunk, r1, r2, sinks};
   a.rows = decode_rows(group);
   if (block_warps != 0 && block_warps != 2 && block_warps != 4)
     LMSF_REFUSE("attention_decode: blocks have 2 or 4 warps, not %d", block_warps);
@@ -670,7 +692,7 @@ static int decode_launch(lmsf::fa::DecodeArgs& a, int gy, int grid_x, int grid_z
 // lmsf_attention_decode_items_scratch_bytes(capacity, n_q_heads), zero when first used.
 LMSF_API int lmsf_attention_decode_build_items(const int* ctx_len, const int* seq_ids, int n_served, int window,
                                                int n_q_heads, int n_kv_heads, int slots, int capacity, void* items,
-                                               void* stream) {
+                                               int chunk, void* stream) {
   using namespace lmsf::fa;
   if (n_served <= 0) return 0;
   if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads)
@@ -678,7 +700,7 @@ LMSF_API int lmsf_attention_decode_build_items(const int* ctx_len, const int* se
   if (capacity < n_served || slots <= 0 || !items || ((uintptr_t)items & 15))
     LMSF_REFUSE("attention_decode_build_items: the list needs room for one entry per request (%d), 16-byte aligned", n_served);
   const int group = n_q_heads / n_kv_heads;
-  ItemArgs a{ctx_len, seq_ids, n_served, window, n_kv_heads * ((group + 15) / 16), slots, capacity, (int4*)items};
+  ItemArgs a{ctx_len, seq_ids, n_served, window, n_kv_heads * ((group + 15) / 16), slots, capacity, (int4*)items, max(chunk, 0)};
   decode_items_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
@@ -692,7 +714,7 @@ LMSF_API int lmsf_attention_decode_items(const void* q, long long q_stride, void
                                          const int* block_table, int max_blocks, const void* items, int capacity,
                                          int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
                                          int n_q_heads, int head_dim, int block_warps, void* scratch, int kv_planes,
-                                         void* stream) {
+                                         int chunk, const float* r1, const float* r2, const float* sinks, void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (capacity <= 0) return 0;
@@ -717,6 +739,8 @@ LMSF_API int lmsf_attention_decode_items(const void* q, long long q_stride, void
     LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = nullptr; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = 1;
+  if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0) LMSF_REFUSE("attention_decode: the distance bias takes both constants; chunk >= 0");
+  a.x = ScoreExtras{chunk, r1, r2, sinks};
   a.rows = decode_rows(group);
   a.items = (const int4*)items;
   a.cluster = 0;
@@ -732,7 +756,7 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
                                    int n_q_heads, int head_dim, int n_splits, void* scratch, void* stream) {
   return lmsf_attention_decode_width(q, q_stride, out, out_stride, cache, page_stride, block_size, n_kv_heads, block_table,
                                      max_blocks, seq_ids, n_served, n_seqs_total, cu_q, ctx_len, scale, window, n_q_heads,
-                                     head_dim, n_splits, 0, scratch, 2, stream);
+                                     head_dim, n_splits, 0, scratch, 2, 0, nullptr, nullptr, nullptr, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

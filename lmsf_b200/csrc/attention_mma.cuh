@@ -60,6 +60,24 @@ __host__ inline bool make_paged_kv(PagedKV& kv, const void* cache, long long pag
   return true;
 }
 
+// What a design may add to the plain causal softmax of the tensor-core kernels; everything is off when zero or null.
+struct ScoreExtras {
+  int chunk;            // > 0: a query at position p sees the keys p - p % chunk .. p only (chunks count from position 0)
+  const float* r1;      // [n_q_heads] with r2: r1 * ln(1 + r2 * (p - key)) is taken off the scaled score
+  const float* r2;
+  const float* sinks;   // [n_q_heads]: exp(sink) is one more term of the softmax's denominator, without a key or a value
+};
+// the first key that a query at position p sees
+__device__ __forceinline__ int first_seen(int p, int window, int chunk) {
+  int lo = window > 0 ? max(0, p - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, p - p % chunk);
+  return lo;
+}
+// the bias in base-2 units: r1 * log2(1 + r2 * distance); lg2.approx is exact to float32 rounding on [1, inf)
+__device__ __forceinline__ float log_distance_bias2(float r1, float r2, int distance) {
+  return r1 * __log2f(fmaf(r2, (float)max(distance, 0), 1.0f));
+}
+
 // Shared-memory stage: TILE rows of K then TILE rows of V.  Every row carries 16 bytes of padding, which
 // makes the 8 rows of an ldmatrix fall into different banks for any HD.  Head size 64 is the exception: its rows
 // are exactly 128 bytes and the 16-byte chunk c of row r sits at chunk c ^ (r & 7) instead, so that a stage is 16 KB

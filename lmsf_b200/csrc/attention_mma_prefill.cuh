@@ -14,6 +14,7 @@ struct PrefillArgs {
   const int* cu_q; const int* ctx_len;
   float scale; int window;
   int n_q_heads, group;
+  ScoreExtras x;
 };
 
 // One block: 64 query tokens (16 per warp) of one head.  Query i of a portion of n tokens of a request
@@ -30,21 +31,24 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
   const int g4 = lane >> 2, t4 = lane & 3;
   const int rows_valid = min(kTileKeys, n - q0);                // query rows of this tile that exist
   const int hi = start + q0 + rows_valid;                       // keys < hi are visible to the tile's last row
-  const int lo = a.window > 0 ? max(0, start + q0 - a.window + 1) : 0;
+  const int lo = first_seen(start + q0, a.window, a.x.chunk);      // the first row's: no row of the tile sees an older key
   const int* table = a.block_table + (size_t)seq * a.max_blocks;
 
   // this thread's two rows
-  int pos[2];
+  int pos[2], row_lo[2];
   bool row_ok[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + g4 + h * 8;
     row_ok[h] = r < rows_valid;
     pos[h] = start + q0 + min(r, rows_valid - 1);
+    row_lo[h] = first_seen(pos[h], a.window, a.x.chunk);
   }
+  const bool biased = a.x.r1 != nullptr;
+  const float r1 = biased ? a.x.r1[head] : 0.f, r2 = biased ? a.x.r2[head] : 0.f;
   const int warp_last_pos = start + q0 + min(warp * 16 + 15, rows_valid - 1);
   const int warp_first_pos = start + q0 + min(warp * 16, rows_valid - 1);
-  const int warp_lo = a.window > 0 ? max(0, warp_first_pos - a.window + 1) : 0;
+  const int warp_lo = first_seen(warp_first_pos, a.window, a.x.chunk);
 
   uint32_t qf[kKSteps][4];
 #pragma unroll
@@ -105,8 +109,9 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + j * 8 + t4 * 2 + (e & 1), h = e >> 1;
-        const bool ok = key <= pos[h] && (a.window <= 0 || key > pos[h] - a.window);
-        const float v = ok ? s[j][e] * sl2 : -INFINITY;
+        const bool ok = key <= pos[h] && key >= row_lo[h];
+        float v = ok ? s[j][e] * sl2 : -INFINITY;
+        if (biased && ok) v -= log_distance_bias2(r1, r2, pos[h] - key);
         s[j][e] = v;
         mx[h] = fmaxf(mx[h], v);
       }
@@ -156,6 +161,8 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
   for (int h = 0; h < 2; ++h) {
     st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
     st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 2);
+    // every row has seen its own key at least, so m is finite; a sink far above it makes the weights vanish
+    if (a.x.sinks) st.l[h] += exp2f(a.x.sinks[head] * kLog2e - st.m[h]);
   }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -177,7 +184,8 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
                                     const void* cache, long long page_stride, int block_size, int n_kv_heads,
                                     const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                     int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
-                                    int n_q_heads, int head_dim, int kv_planes, void* stream) {
+                                    int n_q_heads, int head_dim, int kv_planes, int chunk, const float* r1,
+                                    const float* r2, const float* sinks, void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (n_tiles <= 0) return 0;
@@ -193,6 +201,8 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
   a.block_table = block_table; a.max_blocks = max_blocks; a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;
   a.group = n_q_heads / n_kv_heads;
+  if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0) LMSF_REFUSE("attention_prefill: the distance bias takes both constants; chunk >= 0");
+  a.x = ScoreExtras{chunk, r1, r2, sinks};
   const int smem = kStages * St::kBytes;
   static bool configured = false;
   if (!configured) {

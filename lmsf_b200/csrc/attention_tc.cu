@@ -86,6 +86,7 @@ struct Args {
   int* error_flag;
   int use_tma;      // k and v tiles come by tensor-map copies (block_size >= 8), else by cp.async
   int rows_box;     // keys per tensor-map copy: min(block_size, 128)
+  ScoreExtras x;    // chunks of positions, a bias that grows with the logarithm of the distance, sinks
 };
 
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
@@ -170,7 +171,7 @@ struct Unit {
     i.q0 = q0 + (two_heads ? 0 : x * BM);
     i.rows = max(0, min(BM, n - i.q0));
     i.hi = start + i.q0 + i.rows;                               // keys < hi are visible to the item's last row
-    i.lo = a.window > 0 ? max(0, start + i.q0 - a.window + 1) : 0;
+    i.lo = first_seen(start + i.q0, a.window, a.x.chunk);       // the first row's: later rows start no earlier
     i.tb = i.lo / BN;
     i.te = (i.hi + BN - 1) / BN;
     return i;
@@ -562,7 +563,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const int u_lo = note->lo, u_hi = note->hi;
       const bool row_ok = row < me.rows;
       const int pos = q_pos0 + min(row, me.rows - 1);                // this thread's query position
-      const int row_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+      const int row_lo = first_seen(pos, a.window, a.x.chunk);
       float m_run = -INFINITY, l_run = 0.f;
       const int my_tiles = me.te - me.tb;
       for (int j = 0; j < my_tiles; ++j) {                           // j counts this item's tiles
@@ -574,12 +575,20 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         const int ju = stage0 + j;                                   // the tile counted over the block's units: its stage
         // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
         // the test is the same for the whole group of warps.
-        const bool need_mask = key0 + BN - 1 > q_pos0 || (a.window > 0 && key0 < q_pos0 + me.rows - a.window);
+        // (the item's last row starts latest: a tile that begins before that start has keys some row does not see)
+        const bool need_mask = key0 + BN - 1 > q_pos0 || key0 < first_seen(q_pos0 + me.rows - 1, a.window, a.x.chunk);
         // the row's 128 scores: four loads in flight, one wait
         float sc[BN];
 #pragma unroll
         for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32_issue(t_s + c0, sc + c0);
         tmem_wait_ld();
+        if (a.x.r1 != nullptr) {
+          // the bias is taken off the raw scores, in their own units (the scale is folded in below, with the maximum);
+          // its constants are read here, tile by tile, so that they hold no register where there is no bias
+          const float r1s = a.x.r1[note->head] / sl2, r2 = a.x.r2[note->head];
+#pragma unroll
+          for (int i = 0; i < BN; ++i) sc[i] -= log_distance_bias2(r1s, r2, pos - (key0 + i));
+        }
         if (need_mask) {      // keys that the row does not see become -inf; most tiles skip the test
 #pragma unroll
           for (int i = 0; i < BN; ++i) {
@@ -670,6 +679,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       if (ok && my_tiles > 0) ok = mbar_wait_f(o_done(x), (uint32_t)(my_units_before & 1), failed);
       if (ok && my_tiles > 0) {
         tc_fence_after();
+        if (a.x.sinks) l_run += exp2f(a.x.sinks[note->head] * kLog2e - m_run);   // m_run is finite: a row sees its own key
         const float inv = 1.0f / l_run;
         bf16* dst = a.out + (size_t)(note->tok0 + note->q0 + row) * a.out_stride + (size_t)note->head * HD;
 #pragma unroll
@@ -742,7 +752,8 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
                                        const void* cache, long long page_stride, long long n_pages, int block_size,
                                        int n_kv_heads, const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                        int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
-                                       int n_q_heads, int head_dim, int* error_flag, int kv_planes, void* stream) {
+                                       int n_q_heads, int head_dim, int* error_flag, int kv_planes, int chunk,
+                                       const float* r1, const float* r2, const float* sinks, void* stream) {
   using namespace lmsf;
   using namespace lmsf::tc;
   if (n_tiles <= 0) return 0;
@@ -762,6 +773,9 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
   a.block_table = block_table; a.max_blocks = max_blocks; a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;
   a.group = n_q_heads / n_kv_heads; a.error_flag = error_flag; a.n_q_tiles = n_tiles;
+  if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0 || (r1 && !(scale > 0.f)))
+    LMSF_REFUSE("attention_prefill_tc: the distance bias takes both constants and a positive scale; chunk >= 0");
+  a.x = ScoreExtras{chunk, r1, r2, sinks};
   // pages of 8 keys and more come by tensor-map copies (a box of rows_box keys starts on a 1024-byte
   // boundary of the swizzled tile); smaller pages by cp.async
   a.rows_box = block_size < BN ? block_size : BN;

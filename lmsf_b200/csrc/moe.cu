@@ -251,6 +251,7 @@ __global__ void __launch_bounds__(256) moe_grouped_kernel(TC* __restrict__ C, co
 
 // out[t, d] = sum_j wts[t, j] * down[pair_row[t, j], d] + sigmoid(gate[t]) * shared[t, d]; the sum runs in the order
 // of the choices, float32.  gate: float32, one value per token at gate[t * gate_stride]; shared and gate may be null.
+// wts null: every weight is 1 (the weights went into the experts already).
 template <typename TD, typename TS, typename TO>
 __global__ void moe_combine_kernel(TO* __restrict__ out, const TD* __restrict__ down, const int* __restrict__ pair_row,
                                    const float* __restrict__ wts, int top, const TS* __restrict__ shared,
@@ -261,7 +262,7 @@ __global__ void moe_combine_kernel(TO* __restrict__ out, const TD* __restrict__ 
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
       const int row = pair_row[(size_t)t * top + j];
-      if (row >= 0) acc = fmaf(wts[(size_t)t * top + j], to_f32(down[(size_t)row * width + d]), acc);
+      if (row >= 0) acc = fmaf(wts ? wts[(size_t)t * top + j] : 1.0f, to_f32(down[(size_t)row * width + d]), acc);
     }
     if (shared) acc = fmaf(g, to_f32(shared[(size_t)t * width + d]), acc);
     out[(size_t)t * width + d] = from_f32<TO>(acc);

@@ -556,7 +556,7 @@ def sample_filtered(out: torch.Tensor, logits: torch.Tensor, temperature: torch.
 
 # ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
 
-MMA_MAX_HEAD_DIM = 128
+MMA_MAX_HEAD_DIM = 256
 
 
 def mma_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
@@ -584,6 +584,20 @@ def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, wha
         raise KernelError(f"{what}: q/out rows must be 4-byte aligned and the cache 16-byte aligned")
 
 
+
+
+def _score_extras(n_q_heads: int, chunk, log_bias, sinks):
+    """(chunk, r1, r2, sinks) as the tensor-core attention kernels take them: what a design adds to the causal softmax.
+    chunk > 0: a query at position p sees the keys p - p % chunk .. p only.  log_bias (r1, r2), float32 [n_q_heads] each:
+    r1 * log(1 + r2 * distance) is taken off the scaled scores.  sinks, float32 [n_q_heads]: exp(sink) is one more term
+    of the softmax's denominator."""
+    r1, r2 = log_bias if log_bias is not None else (None, None)
+    _per_head(r1, n_q_heads, "the logarithmic bias")
+    _per_head(r2, n_q_heads, "the logarithmic bias")
+    _per_head(sinks, n_q_heads, "sinks")
+    if chunk is not None and int(chunk) < 0:
+        raise KernelError(f"attention: a chunk of {chunk} positions")
+    return int(chunk or 0), _ptr(r1), _ptr(r2), _ptr(sinks)
 
 
 _DECODE_WIDTHS = {}
@@ -677,14 +691,17 @@ def attention_decode_scratch_floats(n_seqs_total: int, n_q_heads: int, n_splits:
 def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      block_size: int, seq_ids: Optional[torch.Tensor], n_served: int, cu_q: torch.Tensor,
                      ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int,
-                     head_dim: int, n_splits: int, scratch: Optional[torch.Tensor], warps: int = 0, kv_planes: int = 2):
+                     head_dim: int, n_splits: int, scratch: Optional[torch.Tensor], warps: int = 0, kv_planes: int = 2,
+                     chunk: int = 0, log_bias=None, sinks: Optional[torch.Tensor] = None):
     """Attention of requests that bring ONE query token each (row cu_q[s] of q), over their ctx_len[s] keys
     in pages.  seq_ids: int32 [n_served] rows of the block table that are served (None: all, in order).
     scratch: float32, at least attention_decode_scratch_floats(...) values when n_splits > 1, all zero when it is
     first used (torch.zeros); the kernel leaves its counters zero, so one buffer serves every later call.
     warps: the width of the blocks, 4 or 2 (decode_plan chooses it with n_splits); 0 leaves it to the kernel.
-    kv_planes 1: the cache holds one vector per token and kv head that is key and value at once."""
+    kv_planes 1: the cache holds one vector per token and kv head that is key and value at once.
+    chunk, log_bias, sinks: see _score_extras."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode", kv_planes)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
     n_total = block_table.shape[0]
     need = attention_decode_scratch_floats(n_total, n_q_heads, n_splits, head_dim)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
@@ -695,11 +712,11 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
     f = _func("attention_mma.cu", "lmsf_attention_decode_width",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
                c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
-               c_int, c_void_p], d)
+               c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_ids, "seq_ids"), n_served, n_total,
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim,
-           n_splits, warps, _ptr(scratch) if need else None, int(kv_planes), _stream())
+           n_splits, warps, _ptr(scratch) if need else None, int(kv_planes), *extras, _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
@@ -714,7 +731,7 @@ def attention_decode_items_scratch_floats(capacity: int, n_q_heads: int, head_di
 
 
 def decode_build_items(items: torch.Tensor, ctx_len: torch.Tensor, seq_ids: Optional[torch.Tensor], n_served: int,
-                       window: int, n_q_heads: int, n_kv_heads: int, head_dim: int, slots: int):
+                       window: int, n_q_heads: int, n_kv_heads: int, head_dim: int, slots: int, chunk: int = 0):
     """Fills `items` (int32 [capacity, 4]) on the device: request s gets ceil(keys_s / T) splits, with T the smallest
     number of keys for which all blocks fit the `slots` blocks that the device holds at a time; entries that are
     left over are padding.  The attention of requests that differ much in length runs over this list
@@ -723,48 +740,53 @@ def decode_build_items(items: torch.Tensor, ctx_len: torch.Tensor, seq_ids: Opti
         raise KernelError("decode_build_items: items must be a contiguous int32 tensor [capacity, 4]")
     d = _mma_defines(head_dim)
     f = _func("attention_mma.cu", "lmsf_attention_decode_build_items",
-              [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p], d)
+              [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p], d)
     rc = f(_i32(ctx_len, "ctx_len"), _i32(seq_ids, "seq_ids"), n_served, int(window or 0), n_q_heads, n_kv_heads,
-           int(slots), items.shape[0], _ptr(items), _stream())
+           int(slots), items.shape[0], _ptr(items), int(chunk or 0), _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
 def attention_decode_items(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                            block_size: int, items: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor,
                            scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int, warps: int,
-                           scratch: torch.Tensor, kv_planes: int = 2):
+                           scratch: torch.Tensor, kv_planes: int = 2, chunk: int = 0, log_bias=None,
+                           sinks: Optional[torch.Tensor] = None):
     """attention_decode with splits per request, over a list made by decode_build_items.  scratch: float32, at
     least attention_decode_items_scratch_floats(capacity, ...) values, zero when first used."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode_items", kv_planes)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
     need = attention_decode_items_scratch_floats(items.shape[0], n_q_heads, head_dim)
     if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
         raise KernelError(f"attention_decode_items: a list of {items.shape[0]} entries needs {need} float32 values of scratch")
     d = _mma_defines(head_dim)
     f = _func("attention_mma.cu", "lmsf_attention_decode_items",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
-               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p], d)
+               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int,
+               c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _ptr(items), items.shape[0], block_table.shape[0],
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim, int(warps),
-           _ptr(scratch), int(kv_planes), _stream())
+           _ptr(scratch), int(kv_planes), *extras, _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
 def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                       ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                      kv_planes: int = 2):
+                      kv_planes: int = 2, chunk: int = 0, log_bias=None, sinks: Optional[torch.Tensor] = None):
     """Attention of prompt portions.  Tile i covers the query tokens tile_q0[i] .. tile_q0[i] + 63 (counted
     inside the portion) of request tile_seq[i]."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill", kv_planes)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
     d = _mma_defines(head_dim)
     f = _func("attention_mma.cu", "lmsf_attention_prefill",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
-               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p], d)
+               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int,
+               c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
-           int(window or 0), n_q_heads, head_dim, int(kv_planes), _stream())
+           int(window or 0), n_q_heads, head_dim, int(kv_planes), *extras, _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
@@ -781,19 +803,21 @@ def tc_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
 def attention_prefill_tc(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                          block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                          ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                         error_flag: Optional[torch.Tensor] = None, kv_planes: int = 2):
+                         error_flag: Optional[torch.Tensor] = None, kv_planes: int = 2, chunk: int = 0, log_bias=None,
+                         sinks: Optional[torch.Tensor] = None):
     """Attention of prompt portions on tcgen05 tensor cores (head size 64 or 128).  Tile i covers the query
     tokens tile_q0[i] .. tile_q0[i] + 127 (counted inside the portion) of request tile_seq[i]."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill_tc", kv_planes)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
     d = _mma_defines(head_dim)[:1]
     f = _func("attention_tc.cu", "lmsf_attention_prefill_tc",
               [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_int, c_int,
                c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p,
-               c_int, c_void_p], d)
+               c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], block_size,
            n_kv_heads, _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
-           int(window or 0), n_q_heads, head_dim, _i32(error_flag, "error_flag"), int(kv_planes), _stream())
+           int(window or 0), n_q_heads, head_dim, _i32(error_flag, "error_flag"), int(kv_planes), *extras, _stream())
     _check(rc, "attention_tc.cu", "lmsf_attention_tc", d)
 
 
@@ -1269,12 +1293,14 @@ def moe_grouped(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gather: Opt
     _check(rc, "moe.cu", "lmsf_moe")
 
 
-def moe_combine(out: torch.Tensor, down: torch.Tensor, pair_row: torch.Tensor, wts: torch.Tensor,
+def moe_combine(out: torch.Tensor, down: torch.Tensor, pair_row: torch.Tensor, wts: Optional[torch.Tensor],
                 shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None):
     """out[t] = sum_j wts[t, j] * down[pair_row[t, j]] + sigmoid(gate[t]) * shared[t].  down: float32 [pairs, width];
-    gate: float32 [n] view (any stride); shared: [n, width] of out's dtype."""
+    gate: float32 [n] view (any stride); shared: [n, width] of out's dtype.  wts None: every weight is 1."""
     n, width = out.shape
-    top = wts.shape[1]
+    top = pair_row.shape[1]
+    if wts is not None and (wts.dtype != torch.float32 or tuple(wts.shape) != (n, top) or not wts.is_contiguous()):
+        raise KernelError("moe: one contiguous float32 weight per (token, choice)")
     if down.dtype != torch.float32 or down.shape[1] != width or not down.is_contiguous() or not out.is_contiguous():
         raise KernelError("moe: down must be contiguous float32 [pairs, width] and out contiguous [n, width]")
     if shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype or not shared.is_contiguous()):

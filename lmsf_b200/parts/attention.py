@@ -121,6 +121,12 @@ class PagedAttention(Mixer):
                 po = o.new_zeros((o.shape[0], H, hd))
                 po[:, :, :dv] = o
                 tensors["o"] = po.reshape(o.shape[0], H * hd).contiguous()
+        if self.head_gate and H % 8 and "qkv" in tensors:
+            # the gate's rows end the merged matrix: zero rows after them keep the product's row stride a multiple of 16
+            # bytes, which the attention kernels ask of the queries they read in place
+            tensors = dict(tensors)
+            t = tensors["qkv"]
+            tensors["qkv"] = torch.cat([t, t.new_zeros((8 - H % 8, t.shape[1]))], 0).contiguous()
         super().set_weights(tensors)
 
     def cache_spec(self) -> Optional[KVCacheSpec]:
@@ -139,9 +145,9 @@ class PagedAttention(Mixer):
             warnings.warn(f"head_dim {self.head_dim} is beyond the tensor-core attention kernels "
                           f"(up to {kernels.MMA_MAX_HEAD_DIM}); bfloat16 attention runs on the generic kernel",
                           RuntimeWarning, stacklevel=2)
-        elif dtype == torch.bfloat16 and (self.softcap or self._slopes() is not None) and not self._masked_fast():
-            warnings.warn("a cap on the attention scores, or a bias on them, is taken by the generic kernel only; "
-                          "bfloat16 attention runs on it", RuntimeWarning, stacklevel=2)
+        elif dtype == torch.bfloat16 and (self.softcap or self._slopes() is not None):
+            warnings.warn("a cap on the attention scores, or a bias that is linear in the distance, is taken by the generic "
+                          "kernel only; bfloat16 attention runs on it", RuntimeWarning, stacklevel=2)
         slopes = self._slopes()
         if slopes is not None and slopes.numel() != self.num_heads:
             raise ValueError(f"{slopes.numel()} slopes for {self.num_heads} query heads")
@@ -152,9 +158,6 @@ class PagedAttention(Mixer):
     def _log_bias(self):
         f = getattr(self.position_encoding, "score_log_bias", None)
         return f() if f is not None else None
-
-    def _masked_fast(self) -> bool:
-        return False
 
     def forward(self, ctx: StepContext, h, cache: LayerCache, then: Optional[NormAfter] = None):
         group = ctx.groups[cache.group]
@@ -180,12 +183,12 @@ class PagedAttention(Mixer):
             k = qkv[:, self.q_size:self.q_size + self.kv_size]
             v = qkv[:, self.q_size + self.kv_size:self.q_size + 2 * self.kv_size]
             if self.head_gate:
-                gate = qkv[:, self.q_size + 2 * self.kv_size:]
+                gate = qkv[:, self.q_size + 2 * self.kv_size:self.q_size + 2 * self.kv_size + self.num_heads]
         else:  # keys and values are another call's: only the queries are needed
             q = matmul_tn(h, self.qkv[:self.q_size], bias=None if self.qkv_bias is None else self.qkv_bias[:self.q_size])
             k = v = None
             if self.head_gate:
-                gate = matmul_tn(h, self.qkv[self.q_size + 2 * self.kv_size:])
+                gate = matmul_tn(h, self.qkv[self.q_size + 2 * self.kv_size:])[:, :self.num_heads]
         if self.position_encoding is not None and fused is None and self._slopes() is None and self._log_bias() is None:
             if self.qk_norm:
                 raise ValueError("a norm of queries and keys goes with a rotary encoding, a bias on the scores or none")
@@ -222,21 +225,25 @@ class PagedAttention(Mixer):
 def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, *, num_heads: int,
                  num_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None, softcap: float = 0.0,
                  slopes: Optional[torch.Tensor] = None, kv_planes: int = 2, chunk: Optional[int] = None,
-                 log_bias=None, gate: Optional[torch.Tensor] = None) -> None:
+                 log_bias=None, gate: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
     """Attention over pages for any mix of tokens.  bfloat16 with a head size up to 128: single tokens go to the
     split-key decode kernel, longer portions to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for
     head sizes 64 and 128, mma.sync otherwise).  Everything else, float32 included, runs on the generic kernel, which is
     also their plain twin.  kv_planes 1: one cached vector per token and kv head is key and value at once (the fast
     kernels only; the caller keeps its own plain kernel for that layout).  chunk: a query sees the keys of its own chunk of
-    positions only; log_bias (r1, r2): r1 * log(1 + r2 * distance) is taken off the scores (both: the generic kernel);
-    gate [n, heads]: the output of head h is multiplied by sigmoid(gate[:, h])."""
-    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and not chunk and \
-            log_bias is None and not ctx.extras.get("force_generic_attention"):
+    positions only; log_bias (r1, r2): r1 * log(1 + r2 * distance) is taken off the scores; sinks [heads]: exp(sink) joins
+    the softmax's denominator (all three: every kernel); gate [n, heads]: the output of head h is multiplied by
+    sigmoid(gate[:, h]) (the generic kernel itself, a small kernel after the fast ones)."""
+    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and \
+            not ctx.extras.get("force_generic_attention"):
+        extras = dict(chunk=chunk or 0, log_bias=log_bias, sinks=sinks)
         if ctx.n_decode_seqs:
             max_ctx = ctx.extras.get("decode_max_ctx")
             if max_ctx is None:
                 max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
             visible = min(max_ctx, window) if window else max_ctx
+            if chunk:
+                visible = min(visible, chunk)
             # the mean matters to the plan only where it is far below the longest context (a graph names its class)
             mean_ctx = ctx.extras.get("decode_mean_ctx")
             if mean_ctx is None:
@@ -257,21 +264,21 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
                 warps, slots = widths[0][0], widths[0][2][0]
                 if len(widths) > 1 and pairs > slots:
                     warps, slots = widths[1][0], widths[1][2][0]
-                key = ("decode_items", num_kv_heads, group_size, slots, window or 0)
+                key = ("decode_items", num_kv_heads, group_size, slots, window or 0, chunk or 0)
                 items = ctx.extras.get(key)
                 if items is None:
                     capacity = kernels.decode_items_capacity(ctx.n_decode_seqs, num_kv_heads, group_size, slots)
                     items = ctx.extras[key] = torch.empty((capacity, 4), dtype=torch.int32, device=q.device)
                     kernels.decode_build_items(items, ctx.ctx_len, None if all_decode else ctx.decode_seq_ids,
                                                ctx.n_decode_seqs, window or 0, num_heads, num_kv_heads,
-                                               head_dim, slots)
+                                               head_dim, slots, chunk=chunk or 0)
                 need = kernels.attention_decode_items_scratch_floats(items.shape[0], num_heads, head_dim)
                 scratch = ctx.extras.get("decode_items_scratch")
                 if scratch is None or scratch.numel() < need:
                     scratch = ctx.extras["decode_items_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
                 kernels.attention_decode_items(out, q, kv, group.block_table, group.block_size, items, ctx.cu_q,
                                                ctx.ctx_len, scale, window or 0, num_heads,
-                                               num_kv_heads, head_dim, warps, scratch, kv_planes=kv_planes)
+                                               num_kv_heads, head_dim, warps, scratch, kv_planes=kv_planes, **extras)
                 splits = None
             else:
                 splits, warps = kernels.decode_plan(ctx.n_decode_seqs, num_kv_heads, group_size, visible,
@@ -286,16 +293,16 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
                                          None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
                                          ctx.ctx_len, scale, window or 0, num_heads,
                                          num_kv_heads, head_dim, splits, scratch if need else None, warps,
-                                         kv_planes=kv_planes)
+                                         kv_planes=kv_planes, **extras)
         if ctx.n_q_tiles and USE_TC_PREFILL and kernels.tc_attention_supported(q.dtype, head_dim):
             kernels.attention_prefill_tc(out, q, kv, group.block_table, group.block_size, ctx.q_tile128_seq,
                                          ctx.q_tile128_q0, ctx.n_q_tiles128, ctx.cu_q, ctx.ctx_len, scale,
                                          window or 0, num_heads, num_kv_heads, head_dim,
-                                         ctx.error_flag, kv_planes=kv_planes)
+                                         ctx.error_flag, kv_planes=kv_planes, **extras)
         elif ctx.n_q_tiles:
             kernels.attention_prefill(out, q, kv, group.block_table, group.block_size, ctx.q_tile_seq,
                                       ctx.q_tile_q0, ctx.n_q_tiles, ctx.cu_q, ctx.ctx_len, scale,
-                                      window or 0, num_heads, num_kv_heads, head_dim, kv_planes=kv_planes)
+                                      window or 0, num_heads, num_kv_heads, head_dim, kv_planes=kv_planes, **extras)
         if gate is not None:
             kernels.head_gate_(out, gate, num_heads, head_dim)
         return
@@ -303,4 +310,4 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
         raise ValueError("the plain attention kernel of keys and values takes a cache of two planes")
     kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
                               scale, window or 0, num_heads, num_kv_heads, head_dim,
-                              softcap=softcap, slopes=slopes, chunk=chunk or 0, log_bias=log_bias, gate=gate)
+                              softcap=softcap, slopes=slopes, chunk=chunk or 0, log_bias=log_bias, gate=gate, sinks=sinks)

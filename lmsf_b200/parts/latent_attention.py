@@ -131,13 +131,13 @@ class LatentAttention(Mixer):
         return matmul_tn(out, self.o)
 
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, gate) -> None:
-        """bfloat16 with a padded rank up to 128: the engine's tensor-core attention kernels (split-key decode, tcgen05
-        or mma.sync prefill) with one kv head of `padded_rank` values whose cached vector is key and value at once;
-        the gate is a small kernel after them.  float32 and larger ranks: the plain kernel, gate included."""
-        if USE_FAST_KERNELS and kernels.mma_attention_supported(q.dtype, self.padded_rank) and not self.has_sink and \
+        """bfloat16 with a padded rank up to 256: the engine's tensor-core attention kernels (split-key decode, tcgen05
+        or mma.sync prefill) with one kv head of `padded_rank` values whose cached vector is key and value at once,
+        sinks included; the gate is a small kernel after them.  float32 and larger ranks: the plain kernel, gate included."""
+        if USE_FAST_KERNELS and kernels.mma_attention_supported(q.dtype, self.padded_rank) and \
                 not ctx.extras.get("force_generic_attention"):
             paged_attend(ctx, out, q, kv, group, num_heads=self.num_heads, num_kv_heads=1, head_dim=self.padded_rank,
-                         scale=self.scale, window=self.window, kv_planes=1)
+                         scale=self.scale, window=self.window, kv_planes=1, sinks=self._sink32)
             if gate is not None:
                 kernels.head_gate_(out, gate, self.num_heads, self.padded_rank)
             return

@@ -74,7 +74,6 @@ class RoutedExperts(FeedForward):
         self.shared_up: Optional[torch.Tensor] = None
         self.shared_down: Optional[torch.Tensor] = None
         self._bias32: Optional[torch.Tensor] = None
-        self._one_weights: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, E, F = self.hidden_size, self.num_experts, self.expert_size
@@ -93,13 +92,6 @@ class RoutedExperts(FeedForward):
 
     def prepare(self, dtype, device) -> None:
         self._bias32 = self.router_bias.float().contiguous() if self.has_router_bias else None
-        self._one_weights = torch.ones(64 * self.top_k, dtype=torch.float32, device=device) if self.weight_on_input else None
-
-    def _ones(self, n: int, k: int, device) -> torch.Tensor:
-        if self._one_weights is None or self._one_weights.numel() < n * k:      # grows outside a graph's capture only
-            self._one_weights = torch.ones(max(n * k, 2 * (self._one_weights.numel() if self._one_weights is not None else 0)),
-                                           dtype=torch.float32, device=device)
-        return self._one_weights[:n * k].view(n, k)
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         n, D, E, K, F = h.shape[0], self.hidden_size, self.num_experts, self.top_k, self.expert_size
@@ -151,7 +143,6 @@ class RoutedExperts(FeedForward):
                 kernels.relu2_(s)
             shared = matmul_tn(s, self.shared_down)
         out = torch.empty((n, D), dtype=h.dtype, device=dev)
-        if self.weight_on_input:
-            wts = self._ones(n, K, dev)                     # the weights are inside the experts already
-        kernels.moe_combine(out, d, pair_row, wts, shared, z[:, E] if self.has_shared_gate else None)
+        # weight_on_input: the weights are inside the experts already
+        kernels.moe_combine(out, d, pair_row, None if self.weight_on_input else wts, shared, z[:, E] if self.has_shared_gate else None)
         return out

@@ -1,0 +1,539 @@
+"""The Bedenex design on the GPU: every mechanism alone against the plain implementation (tests/plain_bedenex.py), then
+whole models through the engine's step function in every way of cutting, long decoding, reuse of pages, and generation."""
+import json
+import math
+import os
+import random
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+import plain_bedenex as P
+import traces
+import util
+from bedenex_configs import BLOCK, CONFIGS
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TDT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+_folders, _oracles = {}, {}
+
+
+def dev(t, dtype=None):
+    return t.to(DEV) if dtype is None else t.to(device=DEV, dtype=dtype)
+
+
+def i32(values):
+    return torch.tensor(values, dtype=torch.int32, device=DEV)
+
+
+def write_model(cfg, w, prefix):
+    from lmsf_b200.weights.safetensors_io import write_safetensors
+    d = tempfile.mkdtemp(prefix=prefix)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(d, "model.safetensors"), [(n, t.dtype, tuple(t.shape)) for n, t in w.items()], lambda n: w[n])
+    return d
+
+
+def folder_of(name, std=None):
+    """(folder with config.json and model.safetensors in bfloat16, the weights as the plain implementation takes them)."""
+    key = (name, std)
+    if key not in _folders:
+        w = P.random_weights(CONFIGS[name], seed=sum(map(ord, name)), std=std, dtype=torch.bfloat16)
+        _folders[key] = (write_model(CONFIGS[name], w, f"lmsf_bed_{name}_"), w)
+    return _folders[key]
+
+
+def oracle(name, reqs, std=None):
+    _, w = folder_of(name, std)
+    out = {}
+    for rid, toks in reqs.items():
+        key = (name, std, tuple(toks))
+        if key not in _oracles:
+            _oracles[key] = P.forward(CONFIGS[name], w, toks, dtype=torch.float64).float().numpy()
+        out[rid] = _oracles[key]
+    return out
+
+
+def requests_for(name, lengths, seed=0):
+    return {f"q{i}": util.random_ids(n, CONFIGS[name]["vocab"], seed + 11 * i) for i, n in enumerate(lengths)}
+
+
+def worst_rel(rows, ref):
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    return max(float(np.abs(row - ref[rid][pos]).max()) for (rid, pos), row in rows.items()) / scale
+
+
+def position_errors(rows, ref):
+    errs = []
+    for (rid, pos), row in rows.items():
+        d = row - ref[rid][pos]
+        d = d - d.mean()
+        errs.append(float(np.sqrt((d ** 2).mean()) / np.sqrt((ref[rid][pos] ** 2).mean())))
+    return np.sort(np.asarray(errs))
+
+
+F32_TOL = 3e-5
+
+
+def assert_close(rows, ref, dtype, what):
+    """float32: every logit within 3e-5 of the largest.  bfloat16: a token whose rounded router scores choose another expert
+    moves far, in every way of cutting alike, so the bound is on the bulk of the positions; what bfloat16 could hide beyond
+    that is tested on the mechanisms alone with inputs made to show it."""
+    if dtype == "float32":
+        assert worst_rel(rows, ref) <= F32_TOL, (what, worst_rel(rows, ref))
+    else:
+        e = position_errors(rows, ref)
+        assert e[len(e) // 2] <= 3e-2 and e[int(0.9 * len(e))] <= 0.15, (what, e[len(e) // 2], e[int(0.9 * len(e))])
+
+
+def _context(seqs, block_size, n_pages, seed, dtype):
+    """A StepContext built by hand for requests (tokens so far, tokens now); pages dealt out of order, the same pages
+    for the same seed."""
+    from lmsf_b200.parts.base import CacheGroupView, StepContext
+    g = torch.Generator().manual_seed(seed)
+    perm = iter(torch.randperm(n_pages, generator=g).tolist())
+    max_blocks = max((a + b + block_size - 1) // block_size for a, b in seqs)
+    table = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
+    pos, seq, cu, ctxl = [], [], [0], []
+    for s, (a, b) in enumerate(seqs):
+        for j in range((a + b + block_size - 1) // block_size):
+            table[s, j] = next(perm)
+        pos += list(range(a, a + b))
+        seq += [s] * b
+        cu.append(cu[-1] + b)
+        ctxl.append(a + b)
+    n = len(pos)
+    dec = [i for i, (_, b) in enumerate(seqs) if b == 1]
+    tiles = lambda size: [(i, q0) for i, (_, b) in enumerate(seqs) if b > 1 for q0 in range(0, b, size)]
+    t64, t128 = tiles(64), tiles(128)
+    return StepContext(n_tokens=n, n_seqs=len(seqs), dtype=dtype, device=torch.device(DEV), token_ids=i32([0] * n),
+                       positions=i32(pos), token_seq=i32(seq), cu_q=i32(cu), ctx_len=i32(ctxl), state_slot=i32(list(range(len(seqs)))),
+                       groups=[CacheGroupView(dev(table), block_size)], q_lens=[b for _, b in seqs], ctx_lens=ctxl,
+                       state_slots=list(range(len(seqs))), error_flag=torch.zeros(1, dtype=torch.int32, device=DEV),
+                       decode_seq_ids=i32(dec or [0]), n_decode_seqs=len(dec),
+                       q_tile_seq=i32([t[0] for t in t64] or [0]), q_tile_q0=i32([t[1] for t in t64] or [0]), n_q_tiles=len(t64),
+                       q_tile128_seq=i32([t[0] for t in t128] or [0]), q_tile128_q0=i32([t[1] for t in t128] or [0]), n_q_tiles128=len(t128))
+
+
+def run_in_cuts(part, cache_shape, h, cuts, bs, tdt, seed=9):
+    """The part's output for a sequence run in portions `cuts` over one fresh cache."""
+    from lmsf_b200.parts.base import LayerCache
+    cache = LayerCache(kv=torch.zeros(cache_shape, dtype=tdt, device=DEV), group=0)
+    outs, done = [], 0
+    for c in cuts:
+        ctx = _context([(done, c)], bs, cache_shape[0], seed, tdt)
+        outs.append(part.forward(ctx, dev(h[done:done + c]), cache).float().cpu())
+        assert int(ctx.error_flag.item()) == 0
+        done += c
+    return torch.cat(outs).double()
+
+
+# ----------------------------------------------------------------------------- mechanisms alone
+
+def chunk_attention_part(m, D, W, tdt, eps=1e-5):
+    from lmsf_b200.parts.attention import PagedAttention
+    from lmsf_b200.parts.rope import LogDistanceBias
+    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    bias = LogDistanceBias(H)
+    bias.set_weights({"r1": dev(W["r1"].float()), "r2": dev(W["r2"].float())})
+    part = PagedAttention(D, H, G, dk, position_encoding=bias, scale=m["scale"], value_dim=dv, qk_norm=True, qk_norm_eps=eps,
+                          qk_norm_weights=False, value_norm=True, chunk=(m.get("mask") or {}).get("size"), head_gate=True)
+    part.set_weights({"qkv": dev(torch.cat([W["q"], W["k"], W["v"], W["g"]]), tdt), "o": dev(W["o"], tdt)})
+    part.prepare(tdt, torch.device(DEV))
+    return part
+
+
+def chunk_attention_weights(g, D, m, gate_std=1.0):
+    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    W = {"q": torch.randn(H * dk, D, generator=g) / math.sqrt(D), "k": torch.randn(G * dk, D, generator=g) / math.sqrt(D),
+         "v": torch.randn(G * dv, D, generator=g) / math.sqrt(D), "g": gate_std * torch.randn(H, D, generator=g) / math.sqrt(D),
+         "o": torch.randn(D, H * dv, generator=g) / math.sqrt(H * dv),
+         "r1": 0.3 + torch.rand(H, generator=g), "r2": 0.2 + torch.rand(H, generator=g)}
+    return {n: t.to(torch.bfloat16).float() for n, t in W.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,dk,dv,chunk,bs", [(4, 2, 16, 24, 12, 8), (4, 1, 64, 48, 50, 16), (2, 2, 128, 128, 96, 32),
+                                                (3, 3, 40, 24, None, 16), (6, 2, 20, 80, 7, 16), (2, 1, 64, 64, 200, 16),
+                                                (5, 5, 144, 130, 33, 16)])
+def test_chunked_attention_in_portions_and_token_by_token(dtype, H, G, dk, dv, chunk, bs):
+    """Unit-RMS queries, keys and values, the logarithmic distance bias, chunks that no page or tile size divides, a gate per
+    head: whole, with the last tokens one by one, and in portions that cut chunks and pages anywhere."""
+    g = torch.Generator().manual_seed(H * 100 + dk)
+    tdt = TDT[dtype]
+    D, T = 56, 281
+    m = {"heads": H, "kv_heads": G, "dim": dk, "vdim": dv, "scale": 2.0 / math.sqrt(dk)}
+    if chunk:
+        m["mask"] = {"size": chunk}
+    W = chunk_attention_weights(g, D, m)
+    h = torch.randn(T, D, generator=g).to(tdt)
+    want = P.chunk_attention_mixer(h.double(), {n: t.double() for n, t in W.items()}, m, 1e-5)
+    part = chunk_attention_part(m, D, W, tdt)
+    shape = (24, 2, G, bs, part.head_dim) if bs >= 16 else (40, 2, G, bs, part.head_dim)
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for cuts in ([T], [T - 40] + [1] * 40, [2, 7, 64, 3, 129, 2, 50, 1, 1, 22]):
+        got = run_in_cuts(part, shape, h, cuts, bs, tdt)
+        err = (got - want).abs().max(dim=1).values
+        assert float(err.max()) <= tol * float(want.abs().max()), (cuts[:3], int(err.argmax()), float(err.max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dk", [64, 48])
+@pytest.mark.parametrize("T,far,seen", [(237, 200, True), (237, 199, False), (237, 207, True), (237, 208, True), (237, 235, True),
+                                        (201, 199, False), (201, 150, False), (30, 0, True), (250, 200, True), (250, 248, True),
+                                        (251, 249, False)])
+def test_a_key_stands_out_just_inside_its_chunk_and_not_just_outside(dtype, dk, T, far, seen):
+    """Queries and keys share their weights, so the token whose input equals the last token's is the key that the last query
+    prefers; its value differs by a column that only values read.  Chunks of 50 positions over pages of 16: the key sits on
+    the chunk's first position, on the last of the chunk before, at a page's edge, next to the query; the query is also the
+    first of its chunk, or in the sequence's first chunk.  Run whole, with the last token alone, and cut right after the key."""
+    g = torch.Generator().manual_seed(T + far)
+    tdt = TDT[dtype]
+    D, H, G, dv, bs = 40, 2, 1, 32, 16
+    m = {"heads": H, "kv_heads": G, "dim": dk, "vdim": dv, "scale": 0.35, "mask": {"size": 50}}
+    W = chunk_attention_weights(g, D, m, gate_std=0.2)
+    W["q"][:, D - 1] = 0
+    W["k"] = W["q"][:dk].clone()
+    W["v"][:, D - 1] = 1.0
+    W["r1"][:] = 0.05                                  # a small bias: the far key weighs about as much as the query's own
+    h = torch.randn(T, D, generator=g)
+    h[far, :D - 1] = h[T - 1, :D - 1]
+    h[:, D - 1] *= 3
+    h[T - 1, D - 1], h[far, D - 1] = 4.0, -4.0             # opposite tags of one size: equal norms, opposite values
+    h = h.to(tdt)
+    Wd = {n: t.double() for n, t in W.items()}
+    want = P.chunk_attention_mixer(h.double(), Wd, m, 1e-5)[T - 1]
+    other = h.clone()
+    other[far, :D - 1] = -other[far, :D - 1]
+    moved = float((P.chunk_attention_mixer(other.double(), Wd, m, 1e-5)[T - 1] - want).abs().max()) / float(want.abs().max())
+    assert (moved > 0.1) == seen, moved                # the key matters exactly when the design lets the query see it
+    part = chunk_attention_part(m, D, W, tdt)
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for cuts in ([T], [T - 1, 1], [far + 1, T - far - 2, 1] if 0 < far < T - 3 else [3, T - 4, 1]):
+        got = run_in_cuts(part, (20, 2, G, bs, part.head_dim), h, cuts, bs, tdt)[-1]
+        assert float((got - want).abs().max()) <= tol * float(want.abs().max()), (cuts, float((got - want).abs().max()))
+
+
+def latent_part(m, D, W, tdt, eps=1e-5):
+    from lmsf_b200.parts.latent_attention import LatentAttention
+    part = LatentAttention(hidden_size=D, num_heads=m["heads"], head_dim=m["dim"], value_dim=m["vdim"], kv_rank=m["kv_rank"], eps=eps,
+                           scale=m["scale"], window=None, gate=False, rope_dim=m["rot_dim"], rope_dims=m["rot"]["dims"],
+                           rope_base=m["rot"]["base"], sink=True)
+    part.set_weights({"qcg": dev(torch.cat([W["q"], W["dkv"]]), tdt), "c_norm": dev(W["dkv.norm"].float()), "uk": dev(W["uk"], tdt),
+                      "uv": dev(W["uv"], tdt), "o": dev(W["o"], tdt), "sink": dev(W["sink"].float())})
+    part.prepare(tdt, torch.device(DEV))
+    return part
+
+
+def latent_weights(g, D, m):
+    H, dk, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    W = {"q": torch.randn(H * (dk + dr), D, generator=g) / math.sqrt(D), "dkv": torch.randn(r + dr, D, generator=g) / math.sqrt(D),
+         "dkv.norm": 1 + 0.2 * torch.randn(r, generator=g), "uk": torch.randn(H * dk, r, generator=g) / math.sqrt(r),
+         "uv": torch.randn(H * dv, r, generator=g) / math.sqrt(r), "sink": torch.randn(H, generator=g) + 1.0,
+         "o": torch.randn(D, H * dv, generator=g) / math.sqrt(H * dv)}
+    return {n: t.to(torch.bfloat16).float() for n, t in W.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,dk,dr,dv,r,bs", [(3, 24, 8, 20, 40, 8), (1, 32, 4, 8, 16, 16), (5, 8, 6, 12, 130, 16), (4, 48, 32, 64, 96, 32),
+                                             (7, 16, 16, 16, 64, 16), (2, 64, 2, 32, 250, 16)])
+def test_latent_attention_with_a_rotated_key_part_and_a_sink(dtype, H, dk, dr, dv, r, bs):
+    """One cached row [c | rotated key part] per token serves every head as key and as value; the sink takes a share of the
+    softmax that shows (without it the output moves by more than a twentieth).  Whole, token by token, in portions."""
+    g = torch.Generator().manual_seed(H * 10 + dr)
+    tdt = TDT[dtype]
+    D, T = 56, 233
+    m = {"heads": H, "dim": dk, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": 1.2 / math.sqrt(dk + dr), "rot": {"dims": dr, "base": 500.0}}
+    W = latent_weights(g, D, m)
+    h = torch.randn(T, D, generator=g).to(tdt)
+    Wd = {n: t.double() for n, t in W.items()}
+    want = P.latent_attention_mixer(h.double(), Wd, m, 1e-5)
+    no_sink = P.latent_attention_mixer(h.double(), dict(Wd, sink=torch.full((H,), -40.0, dtype=torch.float64)), m, 1e-5)
+    assert float((no_sink - want).abs().max()) > 0.05 * float(want.abs().max())
+    part = latent_part(m, D, W, tdt)
+    shape = (40 if bs == 8 else 20, 1, 1, bs, part.padded_rank)
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for cuts in ([T], [T - 35] + [1] * 35, [2, 7, 64, 3, 129, 2, 1, 1, 24]):
+        got = run_in_cuts(part, shape, h, cuts, bs, tdt)
+        err = (got - want).abs().max(dim=1).values
+        assert float(err.max()) <= tol * float(want.abs().max()), (cuts[:3], int(err.argmax()), float(err.max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 1, 15, 16, 17, 255, 256, 300, 417])
+def test_latent_attention_finds_a_key_far_back_at_and_around_page_borders(dtype, far):
+    """The plain query values read, head by head, twice the rows of the down projection and the key expansion is the
+    identity, so a token whose input equals the last token's is the key the last query prefers among hundreds; the value
+    expansion reads cached values that a tag column alone sets.  The rotated parts weigh little, so the match survives any
+    distance."""
+    g = torch.Generator().manual_seed(far)
+    tdt = TDT[dtype]
+    D, H, dk, dr, dv, T, bs = 40, 2, 32, 8, 24, 420, 16
+    r = H * dk + 16
+    m = {"heads": H, "dim": dk, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": 0.5, "rot": {"dims": dr, "base": 10000.0}}
+    W = latent_weights(g, D, m)
+    W["dkv"][:, D - 1] = 0
+    W["dkv"][H * dk:r] = 0
+    W["dkv"][H * dk:r, D - 1] = 0.1 * torch.randn(16, generator=g)       # these cached values carry the tag alone
+    W["dkv"][r:] *= 0.05
+    W["dkv.norm"][:] = 1.0
+    q = W["q"].view(H, dk + dr, D)
+    q[:, :dk] = 2.0 * W["dkv"][:H * dk].view(H, dk, D)
+    q[:, dk:] *= 0.05
+    W["uk"] = torch.zeros(H * dk, r)
+    W["uk"][:, :H * dk] = torch.eye(H * dk)
+    W["uv"][:, :H * dk] = 0
+    W["uv"][:, H * dk:] *= 10.0
+    W["sink"][:] = 0.5
+    W = {n: t.to(torch.bfloat16).float() for n, t in W.items()}
+    h = torch.randn(T, D, generator=g)
+    h[far, :D - 1] = h[T - 1, :D - 1]
+    h[:, D - 1] *= 3
+    h[T - 1, D - 1], h[far, D - 1] = 4.0, -4.0             # opposite tags of one size: equal norms, opposite values
+    h = h.to(tdt)
+    Wd = {n: t.double() for n, t in W.items()}
+    want = P.latent_attention_mixer(h.double(), Wd, m, 1e-5)[T - 1]
+    other = h.clone()
+    other[far, :D - 1] = -other[far, :D - 1]
+    miss = P.latent_attention_mixer(other.double(), Wd, m, 1e-5)[T - 1]
+    assert float((want - miss).abs().max()) > 0.1 * float(want.abs().max())          # the far key matters
+    part = latent_part(m, D, W, tdt)
+    tol = 5e-5 if dtype == "float32" else 3e-2
+    for cuts in ([T], [T - 1, 1], [far + 1, T - far - 2, 1] if 0 < far < T - 3 else [3, T - 4, 1]):
+        got = run_in_cuts(part, (30, 1, 1, bs, part.padded_rank), h, cuts, bs, tdt)[-1]
+        assert float((got - want).abs().max()) <= tol * float(want.abs().max()), (cuts, float((got - want).abs().max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n,E,top,ff", [(70, 5, 2, 40), (3, 1, 1, 16), (150, 8, 8, 24), (9, 12, 3, 72), (1, 6, 1, 8)])
+def test_experts_read_their_input_times_the_score(dtype, n, E, top, ff):
+    """Sigmoid scores, the largest `top` chosen, not renormalized, multiplied into what the expert reads.  The inputs are large
+    enough that silu is far from linear, so a weight on the output instead would show."""
+    from lmsf_b200.parts.moe import RoutedExperts
+    g = torch.Generator().manual_seed(n + E)
+    D = 48
+    tdt = TDT[dtype]
+    f = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": ff}}
+    W = {"router": torch.randn(E, D, generator=g) * 0.3}
+    for e in range(E):
+        W[f"e{e}.gate"], W[f"e{e}.up"], W[f"e{e}.down"] = (torch.randn(ff, D, generator=g) / 3, torch.randn(ff, D, generator=g) / 7,
+                                                           torch.randn(D, ff, generator=g) / 6)
+    W = {k: v.to(tdt) for k, v in W.items()}
+    h = torch.randn(n, D, generator=g).to(tdt)
+    part = RoutedExperts(hidden_size=D, num_experts=E, top_k=top, expert_size=ff, activation="silu", router_bias=False,
+                         shared_gate=False, routing="sigmoid_top", weight_on_input=True)
+    part.set_weights({"up": dev(torch.cat([W[f"e{e}.{w}"] for e in range(E) for w in ("gate", "up")])),
+                      "down": dev(torch.cat([W[f"e{e}.down"] for e in range(E)])), "router": dev(W["router"])})
+    part.prepare(tdt, torch.device(DEV))
+    got = part.forward(None, dev(h)).float().cpu().double()
+    Wd = {k: v.double() for k, v in W.items()}
+    want = P.moe_feed_forward(h.double(), Wd, f)
+    s = P.sigmoid(h.double() @ Wd["router"].T)
+    val, idx = torch.topk(s, top, dim=-1)
+    outside = torch.zeros_like(want)
+    for t in range(n):
+        for j in range(top):
+            e = int(idx[t, j])
+            outside[t] += val[t, j] * ((P.silu(h[t].double() @ Wd[f"e{e}.gate"].T) * (h[t].double() @ Wd[f"e{e}.up"].T)) @ Wd[f"e{e}.down"].T)
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    if dtype == "float32" and n > 1:
+        assert float((outside - want).abs().max()) > 1e-2 * float(want.abs().max())
+    assert float((got - want).abs().max()) <= tol * float(want.abs().max())
+
+
+def test_both_branches_read_one_norm_and_pass_their_gates():
+    """One layer through the block: x + sigmoid(W1 h + b1) * mixer(h) + sigmoid(W2 h + b2) * ff(h) in a float32 stream, seen
+    through the model's hook after every run of a layer, the span's passes included."""
+    from lmsf_b200.engine.factory import build_model
+    from lmsf_b200.engine.model_runner import ModelRunner, StepEntry
+    folder, w = folder_of("X")
+    toks = util.random_ids(37, CONFIGS["X"]["vocab"], 4)
+    want = []
+    P.forward(CONFIGS["X"], w, toks, dtype=torch.float64, streams=want)
+    model, _, tdt = build_model(folder, "float32", DEV)
+    runner = ModelRunner(model, tdt, torch.device(DEV), 8, num_blocks=32, max_num_seqs=2)
+    mgr = runner.make_cache_manager()
+    got = []
+    model.layer_hook = lambda j, x, res: got.append(res.clone())
+    mgr.add("a")
+    runner.step([StepEntry("a", toks, [])], mgr)
+    model.layer_hook = None
+    assert len(got) == len(want) == 6
+    for j, (a, b) in enumerate(zip(got, want)):
+        assert float((a.cpu().double() - b).abs().max()) <= 2e-5 * float(b.abs().max()), j
+
+
+# ----------------------------------------------------------------------------- whole models through the step function
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["X", "Y", "Z"])
+def test_every_way_of_cutting_agrees_with_the_plain_implementation(name, dtype):
+    """Whole prompts, prefill then token by token, portions of several sizes down to two tokens, and batches of unequal
+    requests with few pages and three live requests (pages are used again)."""
+    folder, _ = folder_of(name)
+    reqs = requests_for(name, [61, 5, 1, 130, 33, 18, 290 if name == "X" else 77])
+    ref = oracle(name, reqs)
+    bs = BLOCK[name]
+    modes = {"whole": traces.whole(reqs), "decode": traces.whole(reqs, tail=30), "portions": traces.portions(reqs, [2, 7, 3, 16, 2, 29]),
+             "pairs": traces.portions(reqs, [2]), "mixed": traces.mixed(reqs, seed=4, max_live=3, tail=10)}
+    got = {}
+    for mode, steps in modes.items():
+        out = traces.run_inprocess(folder, dtype, steps, bs, traces.max_live_tokens(steps, 64), max_live=3)
+        got[mode] = traces.collect(steps, out)
+        assert len(got[mode]) == sum(len(t) for t in reqs.values())
+        assert_close(got[mode], ref, dtype, mode)
+    if dtype == "float32":                            # a position's logits do not depend on the cut beyond rounding
+        for mode in modes:
+            for key, row in got[mode].items():
+                assert np.abs(row - got["whole"][key]).max() <= 2e-5 * np.abs(got["whole"][key]).max(), (mode, key)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_passes_chunks_and_pages_and_replays_graphs(dtype):
+    """A short prompt, then 150 single tokens over many pages and several chunks of both attention layers; the decode steps
+    are replayed from a CUDA graph and must equal the eager steps."""
+    from lmsf_b200.engine.factory import build_model
+    from lmsf_b200.engine.model_runner import ModelRunner, StepEntry
+    folder, _ = folder_of("X")
+    reqs = requests_for("X", [160, 158], seed=3)
+    ref = oracle("X", reqs)
+    model, _, tdt = build_model(folder, dtype, DEV)
+    assert all(getattr(p, "graph_safe", False) for p, _ in model.parts_with_specs())
+    rows = {}
+    for eager in (False, True):
+        runner = ModelRunner(model, tdt, torch.device(DEV), 8, num_blocks=48, max_num_seqs=3, enforce_eager=eager)
+        mgr = runner.make_cache_manager()
+        for rid in reqs:
+            mgr.add(rid)
+        runner.step([StepEntry(rid, reqs[rid][:8], []) for rid in reqs], mgr)
+        got = {rid: [] for rid in reqs}
+        for t in range(8, 158):
+            lg = runner.step([StepEntry(rid, [reqs[rid][t]], [0]) for rid in reqs], mgr)
+            for j, rid in enumerate(reqs):
+                got[rid].append(lg[j].float().cpu().numpy())
+        assert (len(runner._graphs) > 0) == (not eager)
+        rows[eager] = got
+        for rid in reqs:
+            mgr.free(rid)
+    for rid in reqs:
+        scale = float(np.abs(ref[rid]).max())
+        for i, (a, b) in enumerate(zip(rows[False][rid], rows[True][rid])):
+            if dtype == "float32":
+                assert np.abs(a - ref[rid][8 + i]).max() <= F32_TOL * scale, (rid, i)
+            assert np.abs(a - b).max() <= 1e-5 * scale
+    if dtype == "bfloat16":
+        e = position_errors({(rid, 8 + i): a for rid in reqs for i, a in enumerate(rows[False][rid])}, ref)
+        assert e[len(e) // 2] <= 3e-2 and e[int(0.9 * len(e))] <= 0.15
+
+
+def test_pages_of_a_finished_request_serve_the_next():
+    """One live request at a time and pages for one: the second request gets the pages of the first, whose keys must not be
+    seen (a chunk's first query sees itself alone, whatever the page held before)."""
+    folder, _ = folder_of("Y")
+    reqs = requests_for("Y", [40, 40, 33], seed=9)
+    ref = oracle("Y", reqs)
+    steps = traces.portions(reqs, [13, 2])
+    out = traces.run_inprocess(folder, "float32", steps, 16, 64, max_live=1)
+    assert worst_rel(traces.collect(steps, out), ref) <= F32_TOL
+
+
+def test_larger_weights_keep_the_comparison_sharp():
+    """With three times the matrices the softmax is peaked, the gates saturate and the experts' silu is far from linear."""
+    folder, _ = folder_of("Z", std=0.3)
+    reqs = requests_for("Z", [90, 17], seed=5)
+    ref = oracle("Z", reqs, std=0.3)
+    steps = traces.mixed(reqs, seed=1, max_live=2, tail=6)
+    out = traces.run_inprocess(folder, "float32", steps, 16, traces.max_live_tokens(steps, 64), max_live=2)
+    assert worst_rel(traces.collect(steps, out), ref) <= 6e-5
+
+
+def test_the_trace_program_runs_the_design():
+    folder, _ = folder_of("Y")
+    reqs = requests_for("Y", [30, 9], seed=2)
+    ref = oracle("Y", reqs)
+    steps = traces.mixed(reqs, seed=3, max_live=2, tail=4)
+    out = traces.run_program(folder, "float32", steps, traces.max_live_tokens(steps, 64))
+    assert worst_rel(traces.collect(steps, out), ref) <= F32_TOL
+
+
+def test_greedy_generation_through_the_engine():
+    """The generation entry point with its scheduler, continuous batching and sampler: greedy tokens in float32 equal
+    those of the plain implementation fed its own tokens back."""
+    from lmsf_b200 import LLM, SamplingParams
+    folder, w = folder_of("X")
+    cfg = CONFIGS["X"]
+    prompts = [util.random_ids(n, cfg["vocab"], 50 + i) for i, n in enumerate([23, 4, 41])]
+    llm = LLM(folder, dtype="float32", block_size=8, num_gpu_blocks=48, max_num_batched_tokens=24, max_num_seqs=3)
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for _ in range(12):
+            lg = P.forward(cfg, w, toks, dtype=torch.float64)[-1]
+            nxt = int(lg.argmax())
+            got = o.outputs[0].token_ids[len(toks) - len(p)]
+            if got != nxt:                             # only a near tie may be decided otherwise
+                assert float(lg[nxt] - lg[got]) <= 1e-4 * float(lg.abs().max())
+            toks.append(got)
+
+
+# ----------------------------------------------------------------------------- random configurations
+
+def random_config(seed):
+    """Sizes that are no multiples of anything in particular, every optional piece present or absent by chance, the two
+    mixers in any order, a span anywhere (or nowhere), values that a hand-made configuration tends to make equal or 1."""
+    from bedenex_configs import attention, dense, latent, moe, with_mlp
+    rng = random.Random(seed)
+    width = rng.choice([40, 56, 72, 104, 136])
+    layers = []
+    for _ in range(rng.randint(1, 4)):
+        if rng.random() < 0.5:
+            kv = rng.randint(1, 3)
+            dim = rng.choice([8, 12, 16, 24, 40, 64, 128])
+            mixer = attention(kv * rng.randint(1, 3), kv, dim, rng.choice([8, 16, 20, 40, 64]), rng.choice([0.1, 0.3, dim ** -0.5]),
+                              rng.choice([None, 1, 5, 16, 31, 64, 100]))
+        else:
+            rot = rng.choice([2, 4, 6, 16, 32])
+            mixer = latent(rng.randint(1, 5), rng.choice([8, 12, 16, 40, 64]), rot, rng.choice([8, 16, 20, 48]),
+                           rng.choice([8, 24, 40, 64, 100, 128, 200]), rng.choice([0.1, 0.25, 0.4]), rng.choice([50.0, 10000.0, 1.0e6]))
+        r = rng.random()
+        if r < 0.2:
+            mlp = None
+        elif r < 0.5:
+            mlp = dense(rng.choice([8, 20, 44, 100]))
+        else:
+            experts = rng.randint(1, 9)
+            mlp = moe(experts, rng.randint(1, experts), rng.choice([8, 12, 20, 40]))
+        layers.append(with_mlp(mixer, mlp))
+    cfg = {"architecture": "Bedenex", "vocab": rng.choice([61, 128, 257]), "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])},
+           "layers": layers}
+    if rng.random() < 0.7:
+        start = rng.randint(0, len(layers) - 1)
+        cfg["loop"] = {"start": start, "stop": rng.randint(start + 1, len(layers)), "times": rng.randint(1, 3)}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configurations(seed):
+    name = f"R{seed}"
+    CONFIGS[name] = random_config(seed)
+    folder, w = folder_of(name)
+    rng = random.Random(seed)
+    reqs = requests_for(name, [rng.randint(1, 150) for _ in range(4)], seed=seed)
+    ref = oracle(name, reqs)
+    # how far the plain implementation itself moves when it is run in float32
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    cond = max(float(np.abs(P.forward(CONFIGS[name], w, toks, dtype=torch.float32).numpy() - ref[rid]).max()) for rid, toks in reqs.items()) / scale
+    bs = rng.choice([8, 16, 32])
+    for dtype in ("float32", "bfloat16"):
+        for steps in (traces.whole(reqs, tail=5), traces.mixed(reqs, seed=seed, max_live=2, tail=4)):
+            out = traces.run_inprocess(folder, dtype, steps, bs, traces.max_live_tokens(steps, 64), max_live=2)
+            rows = traces.collect(steps, out)
+            if dtype == "float32":
+                assert worst_rel(rows, ref) <= max(5e-5, 3 * cond), (CONFIGS[name], worst_rel(rows, ref), cond)
+            else:
+                e = position_errors(rows, ref)
+                assert e[len(e) // 2] <= 4e-2, (CONFIGS[name], e[len(e) // 2])
