@@ -77,6 +77,11 @@ __device__ __forceinline__ int first_seen(int p, int window, int chunk) {
 __device__ __forceinline__ float log_distance_bias2(float r1, float r2, int distance) {
   return r1 * __log2f(fmaf(r2, (float)max(distance, 0), 1.0f));
 }
+// the same for a distance that is a float already: a thread converts one distance per tile and row and steps from it by
+// constants, which leaves the logarithm and the exponential as the only special-function operations per score
+__device__ __forceinline__ float log_distance_bias2f(float r1, float r2, float distance) {
+  return r1 * __log2f(fmaf(r2, fmaxf(distance, 0.f), 1.0f));
+}
 
 // Shared-memory stage: TILE rows of K then TILE rows of V.  Every row carries 16 bytes of padding, which
 // makes the 8 rows of an ldmatrix fall into different banks for any HD.  Head size 64 is the exception: its rows

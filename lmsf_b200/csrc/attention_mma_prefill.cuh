@@ -104,6 +104,8 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
       }
     }
     float mx[2] = {-INFINITY, -INFINITY};
+    // the distance of this thread's first key of the tile from each of its rows, converted once (exact below 2^24)
+    const float dist0[2] = {(float)(pos[0] - key0 - t4 * 2), (float)(pos[1] - key0 - t4 * 2)};
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
         const int key = key0 + j * 8 + t4 * 2 + (e & 1), h = e >> 1;
         const bool ok = key <= pos[h] && key >= row_lo[h];
         float v = ok ? s[j][e] * sl2 : -INFINITY;
-        if (biased && ok) v -= log_distance_bias2(r1, r2, pos[h] - key);
+        if (biased && ok) v -= log_distance_bias2f(r1, r2, dist0[h] - (float)(j * 8 + (e & 1)));
         s[j][e] = v;
         mx[h] = fmaxf(mx[h], v);
       }

@@ -63,6 +63,7 @@ constexpr int kHB = HD / 64;               // 64-wide blocks of the head dimensi
 constexpr int kStages = LMSF_TC_STAGES;    // k tiles in flight, and v tiles
 constexpr int kQBytes = kHB * BM * 128;    // one item's queries
 constexpr int kKBytes = kHB * BN * 128;    // one k (or v) tile
+constexpr int kBiasEntries = 32 + BN;     // distances at which a warp's 32 rows meet a tile's keys: 31 + BN, rounded up
 constexpr int kOffK = 2 * kQBytes, kOffV = kOffK + kStages * kKBytes;
 constexpr int kSmemBytes = kOffV + kStages * kKBytes + 1024;   // + slack for the 1024-byte alignment
 static_assert(kSmemBytes <= 227 * 1024, "too many stages for the shared memory of an SM");
@@ -226,6 +227,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   // announces the unit's queries on q_full[x]; two slots per item, used in turn.
   struct __align__(16) UnitNote { int head, q0, rows, tb, te, start, tok0, tile_begin, lo, hi, tiles_before, last; };
   __shared__ UnitNote notes[2][2];
+  __shared__ float bias_tbl[8][kBiasEntries];      // per softmax warp: the distance bias of a tile (see the softmax loop)
   volatile int* failed = &failed_mem;
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;     // the swizzle pattern is a function of the address
   const uint32_t sQ = smem, sK = smem + kOffK, sV = smem + kOffV;
@@ -583,11 +585,22 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32_issue(t_s + c0, sc + c0);
         tmem_wait_ld();
         if (a.x.r1 != nullptr) {
-          // the bias is taken off the raw scores, in their own units (the scale is folded in below, with the maximum);
-          // its constants are read here, tile by tile, so that they hold no register where there is no bias
+          // The bias is taken off the raw scores, in their own units (the scale is folded in below, with the maximum).
+          // It depends on the distance alone, and the 32 rows of a warp meet the tile's 128 keys at 159 distances: the
+          // warp computes those once (five logarithms a thread instead of 128) into its own table, and every score
+          // costs a shared-memory load and a subtraction.  Entry t is the distance (first row of the warp) - (last key
+          // of the tile) + t; row l and key i meet at t = l + BN - 1 - i, so the lanes of a warp read consecutive words.
+          // The constants are read here, tile by tile, so that they hold no register where there is no bias.
           const float r1s = a.x.r1[note->head] / sl2, r2 = a.x.r2[note->head];
+          float* tbl = bias_tbl[warp];
+          const int d_first = q_pos0 + (row & ~31) - key0 - (BN - 1);
+          __syncwarp();                                                // the tile before has been read
 #pragma unroll
-          for (int i = 0; i < BN; ++i) sc[i] -= log_distance_bias2(r1s, r2, pos - (key0 + i));
+          for (int t = lane; t < kBiasEntries; t += 32) tbl[t] = log_distance_bias2(r1s, r2, d_first + t);
+          __syncwarp();
+          const float* mine = tbl + lane + (BN - 1);
+#pragma unroll
+          for (int i = 0; i < BN; ++i) sc[i] -= mine[-i];
         }
         if (need_mask) {      // keys that the row does not see become -inf; most tiles skip the test
 #pragma unroll
