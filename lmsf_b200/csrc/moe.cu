@@ -290,6 +290,41 @@ __global__ void moe_weighted_glu_kernel(T* __restrict__ out, const T* __restrict
   }
 }
 
+// the same on bfloat16 rows of a multiple of 8 values, 16 bytes a load
+template <int ACT>
+__global__ void moe_weighted_glu8_kernel(bf16* __restrict__ out, const bf16* __restrict__ y, const int* __restrict__ pair_row,
+                                         const float* __restrict__ wts, int F) {
+  const int pair = blockIdx.x;
+  const int row = pair_row[pair];
+  if (row < 0) return;
+  const float w = wts ? wts[pair] : 1.0f;
+  const uint4* yr = reinterpret_cast<const uint4*>(y + (size_t)row * 2 * F);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * F);
+  const int n8 = F / 8;
+  for (int i = threadIdx.x; i < n8; i += blockDim.x) {
+    const uint4 gv = yr[i], uv = yr[n8 + i];
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 gf = __bfloat1622float2(g2[k]), uf = __bfloat1622float2(u2[k]);
+      float r[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float g = w * (e ? gf.y : gf.x), u = w * (e ? uf.y : uf.x);
+        float a;
+        if (ACT == 0) a = g / (1.0f + expf(-g));
+        else a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        r[e] = a * u;
+      }
+      o2[k] = __floats2bfloat162_rn(r[0], r[1]);
+    }
+    dst[i] = ov;
+  }
+}
+
 template <typename T>
 __global__ void relu2_kernel(T* __restrict__ x, long long n) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -394,7 +429,13 @@ LMSF_API int lmsf_moe_weighted_glu(void* out, const void* y, const int* pair_row
   const int threads = F >= 256 ? 256 : 128;
 #define LMSF_GO(T, A) moe_weighted_glu_kernel<T, A><<<pairs, threads, 0, s>>>((T*)out, (const T*)y, pair_row, wts, F)
   if (dtype == LMSF_F32) { if (act) LMSF_GO(float, 1); else LMSF_GO(float, 0); }
-  else if (dtype == LMSF_BF16) { if (act) LMSF_GO(bf16, 1); else LMSF_GO(bf16, 0); }
+  else if (dtype == LMSF_BF16) {
+    if (F % 8 == 0 && ((uintptr_t)out | (uintptr_t)y) % 16 == 0) {
+      const int t8 = F >= 2048 ? 256 : 128;
+      if (act) moe_weighted_glu8_kernel<1><<<pairs, t8, 0, s>>>((bf16*)out, (const bf16*)y, pair_row, wts, F);
+      else moe_weighted_glu8_kernel<0><<<pairs, t8, 0, s>>>((bf16*)out, (const bf16*)y, pair_row, wts, F);
+    } else if (act) LMSF_GO(bf16, 1); else LMSF_GO(bf16, 0);
+  }
   else LMSF_REFUSE("moe: unknown dtype code %d", dtype);
 #undef LMSF_GO
   return LMSF_LAUNCH_STATUS();

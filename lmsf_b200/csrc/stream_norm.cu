@@ -269,6 +269,28 @@ __global__ void stream_concat_kernel(T* __restrict__ out, const float* __restric
   out[i] = from_f32<T>(c < hidden ? a[t * hidden + c] : b[t * hidden + c - hidden]);
 }
 
+// the same, four values a thread (hidden a multiple of 4, all pointers 16-byte aligned): i counts groups of four
+template <typename T>
+__global__ void stream_concat4_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                      int hidden, long long n4) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const int q = hidden / 4;
+  const long long t = i / (2 * q);
+  const int c = (int)(i % (2 * q));
+  const float4 v = c < q ? reinterpret_cast<const float4*>(a)[t * q + c] : reinterpret_cast<const float4*>(b)[t * q + c - q];
+  T* dst = out + i * 4;
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(dst) = v;
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<unsigned*>(&lo);
+    packed.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+  }
+}
+
 template <typename T, int PER, int V>
 static int launch_gated(float* res, const float* z, long long ldz, const float* b, const void* y1, const void* y2, void* h,
                         const float* w_next, int n, int hidden, float eps_next, cudaStream_t s) {
@@ -365,8 +387,15 @@ LMSF_API int lmsf_stream_concat(void* out, const float* a, const float* b, int n
   if (n <= 0) return 0;
   if (hidden <= 0) LMSF_REFUSE("stream_concat: width %d", hidden);
   const long long count = 2LL * n * hidden;
-  const unsigned blocks = (unsigned)((count + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("stream_concat: unknown dtype code %d", dtype);
+  if (hidden % 4 == 0 && ((uintptr_t)out | (uintptr_t)a | (uintptr_t)b) % 16 == 0) {
+    const unsigned blocks4 = (unsigned)((count / 4 + 255) / 256);
+    if (dtype == LMSF_F32) stream_concat4_kernel<float><<<blocks4, 256, 0, s>>>((float*)out, a, b, hidden, count / 4);
+    else stream_concat4_kernel<bf16><<<blocks4, 256, 0, s>>>((bf16*)out, a, b, hidden, count / 4);
+    return LMSF_LAUNCH_STATUS();
+  }
+  const unsigned blocks = (unsigned)((count + 255) / 256);
   if (dtype == LMSF_F32) stream_concat_kernel<float><<<blocks, 256, 0, s>>>((float*)out, a, b, hidden, count);
   else if (dtype == LMSF_BF16) stream_concat_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, a, b, hidden, count);
   else LMSF_REFUSE("stream_concat: unknown dtype code %d", dtype);

@@ -348,6 +348,18 @@ def test_experts_read_their_input_times_the_score(dtype, n, E, top, ff):
     assert float((got - want).abs().max()) <= tol * float(want.abs().max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n,D", [(5, 50), (70, 52), (1, 8), (33, 130)])
+def test_two_streams_side_by_side_feed_the_entry_of_a_span(dtype, n, D):
+    """[stream | embedding output] in the activation type, for widths that four divides (four values a thread) and others."""
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(n)
+    a, b = torch.randn(n, D, generator=g), torch.randn(n, D, generator=g)
+    out = torch.empty(n, 2 * D, dtype=TDT[dtype], device=DEV)
+    kernels.stream_concat(out, dev(a), dev(b))
+    assert torch.equal(out.cpu(), torch.cat([a, b], 1).to(TDT[dtype]))
+
+
 def test_both_branches_read_one_norm_and_pass_their_gates():
     """One layer through the block: x + sigmoid(W1 h + b1) * mixer(h) + sigmoid(W2 h + b2) * ff(h) in a float32 stream, seen
     through the model's hook after every run of a layer, the span's passes included."""
