@@ -226,7 +226,7 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
                  num_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None, softcap: float = 0.0,
                  slopes: Optional[torch.Tensor] = None, kv_planes: int = 2, chunk: Optional[int] = None,
                  log_bias=None, gate: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
-    """Attention over pages for any mix of tokens.  bfloat16 with a head size up to 128: single tokens go to the
+    """Attention over pages for any mix of tokens.  bfloat16 with a head size up to 256: single tokens go to the
     split-key decode kernel, longer portions to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for
     head sizes 64 and 128, mma.sync otherwise).  Everything else, float32 included, runs on the generic kernel, which is
     also their plain twin.  kv_planes 1: one cached vector per token and kv head is key and value at once (the fast
