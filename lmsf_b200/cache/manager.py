@@ -9,7 +9,7 @@ table per request, pages claimed as the request grows and given back when it end
   window of them); each group has a pool and block tables of its own;
 * for a window group the pages that every future query has passed are given back at `commit`
   and their table entries become -1 (the reference instead reuses table entries as a ring,
-  block_manager.rs:129-135, :165-175);
+  block_manager.rs:129-135, :165-175); a window group may keep the pages of a request's first positions for good;
 * beside the pages each request holds one slot for state of fixed size, claimed at `add` and
   released at `free`; slots claimed since the last call of `take_fresh_slots` must be zeroed by
   the caller before they are used.
@@ -34,8 +34,10 @@ class OutOfPages(RuntimeError):
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """One group of layers with the same needs.  window None: all keys are kept."""
+    """One group of layers with the same needs.  window None: all keys are kept.  keep_first n (with a window): the
+    pages of the request's first n positions are never given back."""
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 class _PoolView:
@@ -71,6 +73,9 @@ class CacheManager:
         self._h = self._lib.lmsf_cm_create(G, windows, blocks, self.block_size, self.num_state_slots)
         if not self._h:
             raise ValueError("the cache manager could not be created from these sizes")
+        for g, spec in enumerate(self.groups):
+            if spec.window and spec.keep_first and self._lib.lmsf_cm_set_keep_first(self._h, g, int(spec.keep_first)) != 0:
+                raise ValueError(f"group {g}: {spec.keep_first} kept first positions were refused")
         self.pools = [_PoolView(self, g) for g in range(G)]
         self._ids: Dict[Hashable, int] = {}
         self._next_id = 1

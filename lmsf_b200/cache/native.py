@@ -16,6 +16,7 @@ def lib():
         l = load_library("host_runtime.cpp")
         sig = {
             "lmsf_cm_create": (c_void_p, [c_int, P_INT, P_INT, c_int, c_int]),
+            "lmsf_cm_set_keep_first": (c_int, [c_void_p, c_int, c_int]),
             "lmsf_cm_destroy": (None, [c_void_p]),
             "lmsf_cm_has": (c_int, [c_void_p, c_int64]),
             "lmsf_cm_can_add": (c_int, [c_void_p]),

@@ -57,7 +57,8 @@ def split_pages(groups: List[GroupLayout], block_size: int, dtype: torch.dtype, 
         return []
     need = []
     for gl in groups:
-        toks = max_model_len if gl.spec.window is None else min(max_model_len, gl.spec.window + 2 * block_size)
+        toks = max_model_len if gl.spec.window is None else \
+            min(max_model_len, gl.spec.window + 2 * block_size + (gl.spec.keep_first + block_size - 1) // block_size * block_size)
         need.append((toks + block_size - 1) // block_size)
     bytes_per_request = sum(n * gl.page_bytes(block_size, dtype) for n, gl in zip(need, groups))
     scale = budget_bytes / max(1, bytes_per_request)
@@ -89,10 +90,18 @@ class CacheStorage:
                 # one slot more than the manager hands out: the "null slot" of a padded batch's stand-in requests
                 lc.state = torch.zeros((num_state_slots + 1, *st.shape), dtype=st.dtype, device=device)
             self.state_tensors.append(lc.state)
+            for role, es in model.call_extra_state_specs(j).items():
+                lc.extra[role] = torch.zeros((num_state_slots + 1, *es.shape), dtype=es.dtype, device=device)
+                self.state_tensors.append(lc.extra[role])
             self.layer_caches.append(lc)
+        # what the embedding keeps per request (the token before a portion, for one)
+        es = model.embedding_state_spec()
+        self.embedding_state = None if es is None else \
+            torch.zeros((num_state_slots + 1, *es.shape), dtype=es.dtype, device=device)
+        self.state_tensors.append(self.embedding_state)
 
     def make_manager(self) -> CacheManager:
-        return CacheManager([GroupSpec(gl.spec.window) for gl in self.groups], self.num_blocks, self.block_size,
+        return CacheManager([GroupSpec(gl.spec.window, gl.spec.keep_first) for gl in self.groups], self.num_blocks, self.block_size,
                             self.num_state_slots)
 
     def zero_state_slots(self, slots: List[int]) -> None:

@@ -198,3 +198,50 @@ LMSF_API int lmsf_scale_softcap(float* x, long long n, float scale, float cap, v
   scale_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, scale, cap);
   return LMSF_LAUNCH_STATUS();
 }
+
+// ---- polynomial activation with a norm per power ------------------------------------------------------------------
+// out[t, i] = a N1(z)_i + b N2(z^2)_i + c N3(z^3)_i + e, where the powers are taken element by element and N divides a
+// token's row of d values by its root mean square, x / sqrt(mean(x^2) + eps): the three sums (of z^2, z^4, z^6) and the
+// factors are float32.  One block per token; the row is read twice (the second time from L1/L2).  coef: float32 [4] =
+// (a, b, c, e) on the device.
+namespace lmsf {
+
+template <typename T>
+__global__ void __launch_bounds__(256) poly_norm_kernel(T* __restrict__ out, const T* __restrict__ in, int d, long long in_stride,
+                                                        const float* __restrict__ coef, float eps) {
+  __shared__ float scratch[3][33];
+  const T* row = in + (size_t)blockIdx.x * in_stride;
+  T* o = out + (size_t)blockIdx.x * d;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float z = to_f32(row[i]), z2 = z * z;
+    s2 += z2;
+    s4 = fmaf(z2, z2, s4);
+    s6 = fmaf(z2 * z2, z2, s6);
+  }
+  s2 = block_sum(s2, scratch[0]);
+  s4 = block_sum(s4, scratch[1]);
+  s6 = block_sum(s6, scratch[2]);
+  const float inv = 1.0f / (float)d;
+  const float f1 = coef[0] / sqrtf(fmaf(s2, inv, eps)), f2 = coef[1] / sqrtf(fmaf(s4, inv, eps)),
+              f3 = coef[2] / sqrtf(fmaf(s6, inv, eps)), e = coef[3];
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float z = to_f32(row[i]), z2 = z * z;
+    o[i] = from_f32<T>(fmaf(f1, z, fmaf(f2, z2, fmaf(f3, z2 * z, e))));
+  }
+}
+
+}  // namespace lmsf
+
+// in: [n, d] with in_stride elements between rows; out: [n, d] contiguous; coef: float32 [4] on the device.
+LMSF_API int lmsf_poly_norm(void* out, const void* in, int n, int d, long long in_stride, const float* coef, float eps,
+                            int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (d <= 0 || in_stride < d || !(eps > 0.f)) LMSF_REFUSE("poly_norm: d=%d, in_stride=%lld, eps=%g", d, in_stride, eps);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) poly_norm_kernel<float><<<n, 256, 0, s>>>((float*)out, (const float*)in, d, in_stride, coef, eps);
+  else if (dtype == LMSF_BF16) poly_norm_kernel<bf16><<<n, 256, 0, s>>>((bf16*)out, (const bf16*)in, d, in_stride, coef, eps);
+  else LMSF_REFUSE("poly_norm: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}

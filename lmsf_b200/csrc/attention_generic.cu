@@ -37,6 +37,9 @@ struct GenericAttnArgs {
   int chunk;                                   // > 0: a query at position p sees the keys from p - p % chunk on (its own chunk of positions)
   const float* log_r1; const float* log_r2;    // [n_q_heads] or null: r1 * log(1 + r2 * (query position - key position)) is taken off the scores
   const float* sinks;                          // [n_q_heads] or null: exp(sink) joins the softmax's denominator, without a key or a value
+  int keep_first;                              // > 0 (with a window): the first keep_first keys of the request stay visible behind the window
+  int sigmoid;                                 // 1: a key's weight is sigmoid(score), not normalised over the keys (no softmax)
+  const float* head_bias;                      // [n_q_heads] or null: a number per query head added to every scaled score
 };
 
 template <typename T>
@@ -52,6 +55,8 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
   const int pos = a.positions[t];
   int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   if (a.chunk > 0) lo = max(lo, pos - pos % a.chunk);
+  const int keep = lo > 0 ? min(a.keep_first, lo) : 0;   // keys 0 .. keep - 1 are seen although the window has passed them
+  const float hb = a.head_bias ? a.head_bias[head] : 0.f;
   const int* table = a.block_table + (size_t)a.token_seq[t] * a.max_blocks;
 
   const T* q = (const T*)a.q + (size_t)t * a.q_stride + (size_t)head * hd;
@@ -67,9 +72,15 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
 
-  for (int tile = lo / 32 + ((warp - lo / 32) % kWarps + kWarps) % kWarps; tile * 32 <= pos; tile += kWarps) {
+  // tiles 0 .. (keep - 1) / 32 hold the kept first keys, tiles lo / 32 .. pos / 32 the window; tile j is always warp j % 4's
+  const int first_tile = keep > 0 ? 0 : lo / 32;
+  for (int tile = first_tile + ((warp - first_tile) % kWarps + kWarps) % kWarps; tile * 32 <= pos; tile += kWarps) {
+    if (tile * 32 >= keep && tile < lo / 32) {   // between the kept keys and the window: on to this warp's first tile of the window
+      tile += (lo / 32 - tile - 1) / kWarps * kWarps;
+      continue;
+    }
     const int key = tile * 32 + lane;
-    const bool valid = key >= lo && key <= pos;
+    const bool valid = (key >= lo || key < keep) && key <= pos;
     long long row = -1;  // element offset of this lane's key row inside the layer's cache
     float s = -INFINITY;
     if (valid) {
@@ -83,7 +94,23 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
         if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
         if (a.slopes) s = fmaf(a.slopes[head], (float)(key - pos), s);
         if (a.log_r1) s -= a.log_r1[head] * logf(1.0f + a.log_r2[head] * (float)(pos - key));
+        s += hb;
       }
+    }
+    if (a.sigmoid) {   // every key on its own: no running maximum, no denominator
+      const float p = row >= 0 ? 1.0f / (1.0f + expf(-s)) : 0.f;
+      for (int j = 0; j < 32; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        const long long rj = __shfl_sync(0xffffffffu, row, j);
+        if (rj < 0) continue;
+        const T* vr = (const T*)a.cache + rj + v_off;
+#pragma unroll
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (i < nd && d < hd) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
+        }
+      }
+      continue;
     }
     const float m_new = fmaxf(m, warp_max(s));
     if (m_new == -INFINITY) continue;  // nothing seen yet (uniform over the warp)
@@ -124,6 +151,10 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
     f[w] = part_m[w] == -INFINITY ? 0.f : expf(part_m[w] - M);
     L = fmaf(part_l[w], f[w], L);
   }
+  if (a.sigmoid) {   // the warps' sums are added as they are, in the order of the warps
+    for (int w = 0; w < kWarps; ++w) f[w] = 1.f;
+    L = 1.f;
+  }
   T* o = (T*)a.out + (size_t)t * a.out_stride + (size_t)head * hd;
   const float g = a.gate ? 1.0f / (1.0f + expf(-to_f32(((const T*)a.gate)[(size_t)t * a.gate_stride + head]))) : 1.0f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
@@ -145,13 +176,17 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
 // chunk > 0: a query at position p sees only the keys of its own chunk of positions, p - p % chunk .. p (chunks are counted
 // from position 0 of the request).  log_r1, log_r2 ([n_q_heads] float32, both or neither): r1 * log(1 + r2 * distance) is
 // taken off the scaled score.  sinks ([n_q_heads] float32 or null): exp(sink[head]) is one more term of the denominator.
-LMSF_API int lmsf_attention_generic_masked(const void* q, long long q_stride, void* out, long long out_stride,
-                                           const void* cache, long long page_stride, const int* block_table, int max_blocks,
-                                           int block_size, const int* token_seq, const int* positions, float scale,
-                                           float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
-                                           int n_kv_heads, int head_dim, int dtype, int shared_kv, const void* gate,
-                                           long long gate_stride, int chunk, const float* log_r1, const float* log_r2,
-                                           const float* sinks, void* stream) {
+// keep_first > 0 (with a window): the request's first keep_first keys stay visible when the window has passed them, at their
+// true positions.  sigmoid = 1: a visible key's weight is sigmoid(score) and the weights are not normalised (no softmax; sinks
+// have no meaning then).  head_bias ([n_q_heads] float32 or null): added to every scaled score of its head.
+LMSF_API int lmsf_attention_generic_weights(const void* q, long long q_stride, void* out, long long out_stride,
+                                            const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                            int block_size, const int* token_seq, const int* positions, float scale,
+                                            float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
+                                            int n_kv_heads, int head_dim, int dtype, int shared_kv, const void* gate,
+                                            long long gate_stride, int chunk, const float* log_r1, const float* log_r2,
+                                            const float* sinks, int keep_first, int sigmoid, const float* head_bias,
+                                            void* stream) {
   using namespace lmsf;
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % 16)
@@ -164,12 +199,27 @@ LMSF_API int lmsf_attention_generic_masked(const void* q, long long q_stride, vo
   if ((log_r1 == nullptr) != (log_r2 == nullptr)) LMSF_REFUSE("attention: the logarithmic bias needs both of its constants");
   GenericAttnArgs a{q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
                     token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim, softcap > 0.f ? softcap : 0.f, slopes,
-                    shared_kv ? 1 : 0, gate, gate_stride, chunk > 0 ? chunk : 0, log_r1, log_r2, sinks};
+                    shared_kv ? 1 : 0, gate, gate_stride, chunk > 0 ? chunk : 0, log_r1, log_r2, sinks,
+                    (window > 0 && keep_first > 0) ? keep_first : 0, sigmoid ? 1 : 0, head_bias};
+  if (sigmoid && sinks) LMSF_REFUSE("attention: sinks belong to a softmax, not to sigmoid weights");
   dim3 grid(n_tokens, n_q_heads);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == LMSF_F32) attention_generic_kernel<float><<<grid, kWarps * 32, 0, s>>>(a);
   else attention_generic_kernel<bf16><<<grid, kWarps * 32, 0, s>>>(a);
   return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_attention_generic_masked(const void* q, long long q_stride, void* out, long long out_stride,
+                                           const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                           int block_size, const int* token_seq, const int* positions, float scale,
+                                           float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
+                                           int n_kv_heads, int head_dim, int dtype, int shared_kv, const void* gate,
+                                           long long gate_stride, int chunk, const float* log_r1, const float* log_r2,
+                                           const float* sinks, void* stream) {
+  return lmsf_attention_generic_weights(q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
+                                        token_seq, positions, scale, softcap, slopes, window, n_tokens, n_q_heads, n_kv_heads,
+                                        head_dim, dtype, shared_kv, gate, gate_stride, chunk, log_r1, log_r2, sinks, 0, 0, nullptr,
+                                        stream);
 }
 
 LMSF_API int lmsf_attention_generic_ext(const void* q, long long q_stride, void* out, long long out_stride,

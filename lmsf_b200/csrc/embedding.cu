@@ -40,6 +40,45 @@ __global__ void embedding_scaled_kernel(T* __restrict__ out, const T* __restrict
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? from_f32<T>(to_f32(src[i]) * scale) : from_f32<T>(0.f);
 }
 
+// out[t, :] = table[id_t, :] * scale + pairs[row_t, :] in float32, where row_t = (id_{t-1} * mul_prev + id_t * mul_cur) mod buckets
+// is chosen by the token and the token before it in the same request, and row `buckets` (the table's last) belongs to a
+// request's first token.  The token before a portion's first token is the request's state: last[slot], one int32 per state
+// slot.  The block of a portion's first token reads it and then stores the portion's last token there; no other block touches
+// that slot, so the launch needs no second pass.  One block per token.
+template <typename T>
+__global__ void embedding_pairs_kernel(float* __restrict__ out, const T* __restrict__ table, const T* __restrict__ pairs,
+                                       const int* __restrict__ ids, const int* __restrict__ positions,
+                                       const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                                       const int* __restrict__ state_slot, int* __restrict__ last, int hidden, int vocab,
+                                       int buckets, long long mul_prev, long long mul_cur, float scale,
+                                       int* __restrict__ error_flag) {
+  __shared__ int s_prev;
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const int seq = token_seq[t];
+  const bool starts = t == cu_q[seq];
+  if (threadIdx.x == 0) {
+    int prev;
+    if (starts) {
+      const int slot = state_slot[seq];
+      prev = last[slot];
+      last[slot] = ids[cu_q[seq + 1] - 1];
+    } else {
+      prev = ids[t - 1];
+    }
+    s_prev = positions[t] == 0 ? -1 : prev;
+  }
+  __syncthreads();
+  const int prev = s_prev;
+  const bool ok = id >= 0 && id < vocab && prev < vocab;
+  if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+  const long long row = prev < 0 ? buckets : ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+  const T* src = table + (size_t)(ok ? id : 0) * hidden;
+  const T* pr = pairs + (size_t)(ok ? row : buckets) * hidden;
+  float* dst = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? fmaf(to_f32(src[i]), scale, to_f32(pr[i])) : 0.f;
+}
+
 // token_ids[dst[i]] = source[src[i]] for every i with dst[i] >= 0: puts tokens that were sampled on the device
 // into the next step's input without a round trip to the host.
 __global__ void patch_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ dst, const int* __restrict__ src,
@@ -91,5 +130,31 @@ LMSF_API int lmsf_embedding_scaled(void* out, const void* table, const int* ids,
     embedding_scaled_kernel<float><<<n_tokens, threads, 0, s>>>((float*)out, (const float*)table, ids, hidden, vocab, scale, error_flag);
   else
     embedding_scaled_kernel<bf16><<<n_tokens, threads, 0, s>>>((bf16*)out, (const bf16*)table, ids, hidden, vocab, scale, error_flag);
+  return LMSF_LAUNCH_STATUS();
+}
+
+// out: float32 [n_tokens, hidden]; table: [vocab, hidden] and pairs: [buckets + 1, hidden] of `dtype`; last: int32, one per
+// state slot (the slot's newest token).  mul_prev, mul_cur >= 0.
+LMSF_API int lmsf_embedding_pairs(float* out, const void* table, const void* pairs, const int* ids, const int* positions,
+                                  const int* token_seq, const int* cu_q, const int* state_slot, int* last, int n_tokens,
+                                  int hidden, int vocab, int buckets, long long mul_prev, long long mul_cur, float scale,
+                                  int dtype, int* error_flag, void* stream) {
+  using namespace lmsf;
+  if (n_tokens <= 0) return 0;
+  if (hidden <= 0 || vocab <= 0 || buckets <= 0 || mul_prev < 0 || mul_cur < 0)
+    LMSF_REFUSE("embedding: hidden=%d vocab=%d buckets=%d and non-negative multipliers", hidden, vocab, buckets);
+  if ((double)vocab * (double)mul_prev + (double)vocab * (double)mul_cur > 9.0e18)
+    LMSF_REFUSE("embedding: the pair index overflows 64 bits");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == LMSF_F32)
+    embedding_pairs_kernel<float><<<n_tokens, threads, 0, s>>>(out, (const float*)table, (const float*)pairs, ids, positions,
+                                                               token_seq, cu_q, state_slot, last, hidden, vocab, buckets,
+                                                               mul_prev, mul_cur, scale, error_flag);
+  else if (dtype == LMSF_BF16)
+    embedding_pairs_kernel<bf16><<<n_tokens, threads, 0, s>>>(out, (const bf16*)table, (const bf16*)pairs, ids, positions,
+                                                              token_seq, cu_q, state_slot, last, hidden, vocab, buckets,
+                                                              mul_prev, mul_cur, scale, error_flag);
+  else LMSF_REFUSE("embedding: unknown dtype code %d", dtype);
   return LMSF_LAUNCH_STATUS();
 }

@@ -51,6 +51,7 @@ struct Request {
 
 struct Manager {
   std::vector<int> windows;               // per group, <= 0: all keys
+  std::vector<int> keep_first;            // per group: a window never passes the request's first keep_first positions
   std::vector<Pool> pools;
   int block_size = 16;
   int n_slots = 0;
@@ -62,6 +63,13 @@ struct Manager {
     const int w = windows[g];
     if (w <= 0) return 0;
     return std::max(0, start - w + 1) / block_size;
+  }
+  // entries below this one hold positions that a window group keeps for the whole life of the request
+  int kept_entries(int g) const { return windows[g] > 0 && keep_first[g] > 0 ? entries_for(keep_first[g]) : 0; }
+  // the most positions of a request of `tokens` tokens that a group holds pages for at one time
+  int held_tokens(int g, int tokens) const {
+    if (windows[g] <= 0) return tokens;
+    return std::min(tokens, windows[g] + 2 * block_size + kept_entries(g) * block_size);
   }
 };
 
@@ -81,6 +89,7 @@ LMSF_HOST_API void* lmsf_cm_create(int n_groups, const int* windows, const int* 
   m->block_size = block_size;
   m->n_slots = n_slots;
   m->windows.assign(windows, windows + n_groups);
+  m->keep_first.assign(n_groups, 0);
   m->pools.resize(n_groups);
   for (int g = 0; g < n_groups; ++g) {
     Pool& p = m->pools[g];
@@ -91,6 +100,14 @@ LMSF_HOST_API void* lmsf_cm_create(int n_groups, const int* windows, const int* 
   }
   for (int s = n_slots - 1; s >= 0; --s) m->free_slots.push_back(s);
   return m;
+}
+
+// The first `n` positions of every request stay cached in window group g (no request may be live yet).
+LMSF_HOST_API int lmsf_cm_set_keep_first(void* h, int g, int n) {
+  Manager& m = *M(h);
+  if (g < 0 || g >= (int)m.pools.size() || n < 0 || !m.reqs.empty()) return -1;
+  m.keep_first[g] = n;
+  return 0;
 }
 
 LMSF_HOST_API void lmsf_cm_destroy(void* h) { delete M(h); }
@@ -183,7 +200,7 @@ LMSF_HOST_API int lmsf_cm_commit(void* h, int64_t rid, int n) {
   for (size_t g = 0; g < m.pools.size(); ++g) {
     if (m.windows[g] <= 0) continue;
     const int first = std::min<int>(m.first_needed_entry((int)g, r.num_tokens), (int)r.tables[g].size());
-    for (int i = 0; i < first; ++i)
+    for (int i = m.kept_entries((int)g); i < first; ++i)
       if (r.tables[g][i] >= 0) {
         if (m.pools[g].release(r.tables[g][i]) != 0) rc = -5;
         r.tables[g][i] = -1;
@@ -429,8 +446,7 @@ void release_request(Sched& s, int64_t rid) {
 bool fits_alone(const Sched& s, int num_tokens) {
   const Manager& m = *s.cm;
   for (size_t g = 0; g < m.pools.size(); ++g) {
-    const int toks = m.windows[g] <= 0 ? num_tokens : std::min(num_tokens, m.windows[g] + 2 * m.block_size);
-    if (m.entries_for(toks) > m.pools[g].n) return false;
+    if (m.entries_for(m.held_tokens((int)g, num_tokens)) > m.pools[g].n) return false;
   }
   return true;
 }

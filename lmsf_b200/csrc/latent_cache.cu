@@ -139,7 +139,34 @@ __global__ void head_gate8_kernel(bf16* __restrict__ x, long long x_stride, cons
   }
 }
 
+// x[t, h, d] *= sigmoid(gate[t, h, d]) for the first `value_dim` values of every head of head_dim values: a gate per element
+// of the concatenated value heads (the gate has no padding, the attention's output may have).
+template <typename T>
+__global__ void value_gate_kernel(T* __restrict__ x, long long x_stride, const T* __restrict__ gate, long long gate_stride,
+                                  int heads, int head_dim, int value_dim) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < heads * value_dim; i += blockDim.x) {
+    const int h = i / value_dim, d = i - h * value_dim;
+    const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * gate_stride + i])));
+    T* p = x + (size_t)t * x_stride + (size_t)h * head_dim + d;
+    *p = from_f32<T>(to_f32(*p) * g);
+  }
+}
+
 }  // namespace lmsf
+
+LMSF_API int lmsf_value_gate(void* x, long long x_stride, const void* gate, long long gate_stride, int n, int heads,
+                             int head_dim, int value_dim, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (heads <= 0 || head_dim <= 0 || value_dim <= 0 || value_dim > head_dim)
+    LMSF_REFUSE("value_gate: heads=%d head_dim=%d value_dim=%d", heads, head_dim, value_dim);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) value_gate_kernel<float><<<n, 256, 0, s>>>((float*)x, x_stride, (const float*)gate, gate_stride, heads, head_dim, value_dim);
+  else if (dtype == LMSF_BF16) value_gate_kernel<bf16><<<n, 256, 0, s>>>((bf16*)x, x_stride, (const bf16*)gate, gate_stride, heads, head_dim, value_dim);
+  else LMSF_REFUSE("value_gate: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}
 
 LMSF_API int lmsf_head_gate(void* x, long long x_stride, const void* gate, long long gate_stride, int n, int heads,
                             int head_dim, int dtype, void* stream) {

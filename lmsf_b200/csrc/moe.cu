@@ -134,6 +134,59 @@ __global__ void moe_topk_sigmoid_kernel(const float* __restrict__ logits, long l
   }
 }
 
+// Routing by a softmax over ALL `outputs` router logits (more outputs than experts: the outputs behind the experts stand for
+// experts that return their input).  s = softmax(logits); the choice is made by s + correction; the weights are the chosen
+// outputs' s times `weight_scale`, not renormalised.  Ties go to the lower number.  One warp per token; shared memory: per
+// warp 2 * outputs floats.
+__global__ void moe_topk_softmax_all_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
+                                            int n, int outputs, int top, float weight_scale, int* __restrict__ ids,
+                                            float* __restrict__ wts) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n) return;
+  float* sc = sm + (size_t)warp * 2 * outputs;    // the scores
+  float* c = sc + outputs;                        // the choice scores
+  float m = -INFINITY;
+  for (int e = lane; e < outputs; e += 32) m = fmaxf(m, logits[(size_t)t * ld + e]);
+  m = warp_max(m);
+  float den = 0.f;
+  for (int e = lane; e < outputs; e += 32) {
+    const float p = expf(logits[(size_t)t * ld + e] - m);
+    sc[e] = p;
+    den += p;
+  }
+  den = warp_sum(den);
+  for (int e = lane; e < outputs; e += 32) {
+    const float v = sc[e] / den;
+    sc[e] = v;
+    c[e] = v + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  int mine_id = 0;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < outputs; e += 32)
+      if (c[e] > best) { best = c[e]; arg = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) arg = 0;                   // nothing left to choose (NaN logits): a fault of the input
+    if (j == lane) mine_id = arg;
+    __syncwarp();
+    if (lane == 0) c[arg] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[(size_t)t * top + lane] = mine_id;
+    wts[(size_t)t * top + lane] = sc[mine_id] * weight_scale;
+  }
+}
+
 // One block.  ids: [pairs]; offsets: [experts + 1]; pair_row: [pairs] row of each pair in expert order;
 // row_token: [pairs] token of each row; tiles: [max_tiles][4] = (expert, first row, rows, 0); meta[0] = number of tiles.
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ ids, int pairs, int top, int experts,
@@ -252,10 +305,12 @@ __global__ void __launch_bounds__(256) moe_grouped_kernel(TC* __restrict__ C, co
 // out[t, d] = sum_j wts[t, j] * down[pair_row[t, j], d] + sigmoid(gate[t]) * shared[t, d]; the sum runs in the order
 // of the choices, float32.  gate: float32, one value per token at gate[t * gate_stride]; shared and gate may be null.
 // wts null: every weight is 1 (the weights went into the experts already).
+// ids with x (both or neither): a choice whose number is `experts` or more is an expert that returns its input, x[t].
 template <typename TD, typename TS, typename TO>
 __global__ void moe_combine_kernel(TO* __restrict__ out, const TD* __restrict__ down, const int* __restrict__ pair_row,
                                    const float* __restrict__ wts, int top, const TS* __restrict__ shared,
-                                   const float* __restrict__ gate, long long gate_stride, int width) {
+                                   const float* __restrict__ gate, long long gate_stride, int width,
+                                   const int* __restrict__ ids, int experts, const TS* __restrict__ x) {
   const int t = blockIdx.x;
   const float g = (shared && gate) ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride])) : 1.0f;
   for (int d = threadIdx.x; d < width; d += blockDim.x) {
@@ -263,6 +318,8 @@ __global__ void moe_combine_kernel(TO* __restrict__ out, const TD* __restrict__ 
     for (int j = 0; j < top; ++j) {
       const int row = pair_row[(size_t)t * top + j];
       if (row >= 0) acc = fmaf(wts ? wts[(size_t)t * top + j] : 1.0f, to_f32(down[(size_t)row * width + d]), acc);
+      else if (ids && ids[(size_t)t * top + j] >= experts)
+        acc = fmaf(wts ? wts[(size_t)t * top + j] : 1.0f, to_f32(x[(size_t)t * width + d]), acc);
     }
     if (shared) acc = fmaf(g, to_f32(shared[(size_t)t * width + d]), acc);
     out[(size_t)t * width + d] = from_f32<TO>(acc);
@@ -357,6 +414,19 @@ LMSF_API int lmsf_moe_topk_sigmoid(const float* logits, long long ld, const floa
   return LMSF_LAUNCH_STATUS();
 }
 
+// logits: float32 [n, ld] of which the first `outputs` columns are the router's; correction: float32 [outputs] or null.
+LMSF_API int lmsf_moe_topk_softmax_all(const float* logits, long long ld, const float* correction, int n, int outputs, int top,
+                                       float weight_scale, int* ids, float* wts, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (outputs <= 0 || outputs > kMaxExperts || top <= 0 || top > outputs || top > 32)
+    LMSF_REFUSE("moe: %d choices of %d router outputs (up to %d outputs, up to 32 choices)", top, outputs, kMaxExperts);
+  const size_t smem = (size_t)4 * 2 * outputs * sizeof(float);
+  moe_topk_softmax_all_kernel<<<ceil_div(n, 4), 128, smem, (cudaStream_t)stream>>>(logits, ld, correction, n, outputs, top,
+                                                                                 weight_scale, ids, wts);
+  return LMSF_LAUNCH_STATUS();
+}
+
 LMSF_API int lmsf_moe_tile_rows() { return lmsf::BM; }
 
 // tile_rows: rows per tile of the product that will walk the list (lmsf_moe_tile_rows() for the kernel of this file).
@@ -393,18 +463,27 @@ LMSF_API int lmsf_moe_grouped(void* C, const void* A, const void* W, const int* 
 }
 
 // out: [n, width] of out_dtype; down: [pairs, width] float32; shared: [n, width] of out_dtype or null.
-LMSF_API int lmsf_moe_combine(void* out, const float* down, const int* pair_row, const float* wts, int top, const void* shared,
-                              const float* gate, long long gate_stride, int n, int width, int out_dtype, void* stream) {
+// ids ([n, top]) and x ([n, width] of out_dtype), both or neither: choices numbered `experts` and up return the token's x.
+LMSF_API int lmsf_moe_combine_identity(void* out, const float* down, const int* pair_row, const float* wts, int top,
+                                       const void* shared, const float* gate, long long gate_stride, int n, int width,
+                                       int out_dtype, const int* ids, int experts, const void* x, void* stream) {
   using namespace lmsf;
   if (n <= 0) return 0;
   if (width <= 0 || top <= 0) LMSF_REFUSE("moe: width=%d top=%d", width, top);
+  if ((ids == nullptr) != (x == nullptr)) LMSF_REFUSE("moe: experts that return their input need the choices and the input");
   cudaStream_t s = (cudaStream_t)stream;
   if (out_dtype == LMSF_F32)
-    moe_combine_kernel<float, float, float><<<n, 256, 0, s>>>((float*)out, down, pair_row, wts, top, (const float*)shared, gate, gate_stride, width);
+    moe_combine_kernel<float, float, float><<<n, 256, 0, s>>>((float*)out, down, pair_row, wts, top, (const float*)shared, gate, gate_stride, width, ids, experts, (const float*)x);
   else if (out_dtype == LMSF_BF16)
-    moe_combine_kernel<float, bf16, bf16><<<n, 256, 0, s>>>((bf16*)out, down, pair_row, wts, top, (const bf16*)shared, gate, gate_stride, width);
+    moe_combine_kernel<float, bf16, bf16><<<n, 256, 0, s>>>((bf16*)out, down, pair_row, wts, top, (const bf16*)shared, gate, gate_stride, width, ids, experts, (const bf16*)x);
   else LMSF_REFUSE("moe: unknown dtype code %d", out_dtype);
   return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_moe_combine(void* out, const float* down, const int* pair_row, const float* wts, int top, const void* shared,
+                              const float* gate, long long gate_stride, int n, int width, int out_dtype, void* stream) {
+  return lmsf_moe_combine_identity(out, down, pair_row, wts, top, shared, gate, gate_stride, n, width, out_dtype, nullptr, 0,
+                                   nullptr, stream);
 }
 
 LMSF_API int lmsf_relu2(void* x, long long n, int dtype, void* stream) {

@@ -401,3 +401,60 @@ LMSF_API int lmsf_stream_concat(void* out, const float* a, const float* b, int n
   else LMSF_REFUSE("stream_concat: unknown dtype code %d", dtype);
   return LMSF_LAUNCH_STATUS();
 }
+
+// ---- token shift ----------------------------------------------------------------------------------------------
+// out[t] = h[t] + (h[t - 1] - h[t]) * mix, element by element, where h[t - 1] is the row of the token before in the same
+// request as it was before this replacement: zeros for a request's first token, and for a portion's first token the row
+// that the request's state slot holds (the last row of its portion before).  The block of a portion's first token reads
+// the slot and then stores the portion's last row there; no other block touches that slot.  float32 inside, one block per
+// token; the slot holds h's values exactly (float32 of what h stores), so a cut changes no bit.
+namespace lmsf {
+
+template <typename T>
+__global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ mix,
+                                   float* __restrict__ state, const int* __restrict__ positions,
+                                   const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                                   const int* __restrict__ state_slot, int hidden) {
+  const int t = blockIdx.x;
+  const int seq = token_seq[t];
+  const int first = cu_q[seq];
+  const bool starts = t == first;
+  const bool zero = positions[t] == 0;
+  const T* cur = h + (size_t)t * hidden;
+  T* dst = out + (size_t)t * hidden;
+  if (starts) {
+    float* slot = state + (size_t)state_slot[seq] * hidden;
+    const T* last = h + (size_t)(cu_q[seq + 1] - 1) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float before = zero ? 0.f : slot[i];
+      const float c = to_f32(cur[i]);
+      slot[i] = to_f32(last[i]);
+      dst[i] = from_f32<T>(fmaf(before - c, mix[i], c));
+    }
+  } else {
+    const T* prev = cur - hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float c = to_f32(cur[i]);
+      dst[i] = from_f32<T>(fmaf((zero ? 0.f : to_f32(prev[i])) - c, mix[i], c));
+    }
+  }
+}
+
+}  // namespace lmsf
+
+// out, h: [n, hidden] of `dtype` (out is not h); mix: float32 [hidden]; state: float32 [slots, hidden].
+LMSF_API int lmsf_token_shift(void* out, const void* h, const float* mix, float* state, const int* positions,
+                              const int* token_seq, const int* cu_q, const int* state_slot, int n, int hidden, int dtype,
+                              void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (hidden <= 0 || out == h) LMSF_REFUSE("token_shift: hidden=%d, and out must not be h", hidden);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == LMSF_F32)
+    token_shift_kernel<float><<<n, threads, 0, s>>>((float*)out, (const float*)h, mix, state, positions, token_seq, cu_q, state_slot, hidden);
+  else if (dtype == LMSF_BF16)
+    token_shift_kernel<bf16><<<n, threads, 0, s>>>((bf16*)out, (const bf16*)h, mix, state, positions, token_seq, cu_q, state_slot, hidden);
+  else LMSF_REFUSE("token_shift: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}

@@ -206,7 +206,8 @@ class ModelRunner:
                           ctx_lens=hb.ctx_lens, state_slots=hb.slots, error_flag=self.error_flag,
                           decode_seq_ids=view("dec_ids"), n_decode_seqs=hb.n_dec, q_tile_seq=view("tile_seq"),
                           q_tile_q0=view("tile_q0"), n_q_tiles=hb.n_tiles, q_tile128_seq=view("tile128_seq"),
-                          q_tile128_q0=view("tile128_q0"), n_q_tiles128=hb.n_tiles128)
+                          q_tile128_q0=view("tile128_q0"), n_q_tiles128=hb.n_tiles128,
+                          embedding_state=self.storage.embedding_state)
         return ctx, view("rows")
 
     def build_context(self, entries: Sequence[StepEntry], mgr: CacheManager) -> Tuple[StepContext, torch.Tensor]:

@@ -121,6 +121,27 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, error_f
     _check(rc, "embedding.cu", "lmsf_embedding")
 
 
+def embedding_pairs(out: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                    token_seq: torch.Tensor, cu_q: torch.Tensor, state_slot: torch.Tensor, last: torch.Tensor, buckets: int,
+                    mul_prev: int, mul_cur: int, scale: float = 1.0, error_flag: Optional[torch.Tensor] = None):
+    """out[t] = table[id_t] * scale + pairs[(id_{t-1} * mul_prev + id_t * mul_cur) mod buckets] in float32; a request's first
+    token takes pairs[buckets].  `last` (int32, one per state slot) holds the token before a portion and receives the
+    portion's last token.  out: float32 [n, hidden]; table [vocab, hidden] and pairs [buckets + 1, hidden] of one dtype."""
+    n, hidden = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or table.shape[1] != hidden or not table.is_contiguous() or \
+            pairs.shape != (buckets + 1, hidden) or pairs.dtype != table.dtype or not pairs.is_contiguous():
+        raise KernelError("embedding_pairs: out float32 [n, hidden], table [vocab, hidden], pairs [buckets + 1, hidden]")
+    if last.dtype != torch.int32 or not last.is_contiguous():
+        raise KernelError("embedding_pairs: the slots' last tokens must be contiguous int32")
+    f = _func("embedding.cu", "lmsf_embedding_pairs",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+               c_int, c_longlong, c_longlong, c_float, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(out), _ptr(table), _ptr(pairs), _i32(ids, "ids"), _i32(positions, "positions"), _i32(token_seq, "token_seq"),
+           _i32(cu_q, "cu_q"), _i32(state_slot, "state_slot"), _ptr(last), n, hidden, table.shape[0], int(buckets),
+           int(mul_prev), int(mul_cur), float(scale), dtype_code(table.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "embedding.cu", "lmsf_embedding")
+
+
 def patch_tokens(token_ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, source: torch.Tensor):
     """token_ids[dst[i]] = source[src[i]] wherever dst[i] >= 0 (all int32, on the device)."""
     f = _func("embedding.cu", "lmsf_patch_tokens", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
@@ -254,6 +275,9 @@ def _per_head(t: Optional[torch.Tensor], heads: int, what: str) -> None:
 _GENERIC_MASKED_ARGS = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
                         c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                         c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+_GENERIC_WEIGHTS_ARGS = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
+                         c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                         c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
 
 
 def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
@@ -261,14 +285,17 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, b
                       n_q_heads: int, n_kv_heads: int, head_dim: int, softcap: float = 0.0,
                       slopes: Optional[torch.Tensor] = None, chunk: int = 0,
                       log_bias: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, sinks: Optional[torch.Tensor] = None,
-                      gate: Optional[torch.Tensor] = None):
+                      gate: Optional[torch.Tensor] = None, keep_first: int = 0, sigmoid: bool = False,
+                      head_bias: Optional[torch.Tensor] = None):
     """out[t] = softmax(scale q[t] K^T) V over the keys lo..positions[t] of token t's request, read from pages.
     q, out: [n, n_q_heads * head_dim] (last dimension contiguous); window <= 0 means all keys; softcap > 0 caps the
     scaled scores smoothly, softcap * tanh(score / softcap); slopes (float32 [n_q_heads]) adds
     slopes[head] * (key position - query position) to the scaled scores.  chunk > 0: a query at position p sees the keys
     p - p % chunk .. p only.  log_bias (r1, r2), float32 [n_q_heads] each: r1 * log(1 + r2 * distance) is taken off the
     scaled scores.  sinks (float32 [n_q_heads]): exp(sink) is one more term of the softmax's denominator.  gate ([n,
-    n_q_heads] view of q's dtype): head h's output is multiplied by sigmoid(gate[t, h])."""
+    n_q_heads] view of q's dtype): head h's output is multiplied by sigmoid(gate[t, h]).  keep_first (with a window): the
+    request's first keep_first keys stay visible behind the window.  sigmoid: a visible key's weight is sigmoid(score), not
+    normalised over the keys.  head_bias (float32 [n_q_heads]): added to every scaled score of its head."""
     n = q.shape[0]
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
         raise KernelError("attention: q and out must be [n, heads * head_dim] with a contiguous last dimension")
@@ -277,17 +304,18 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, b
         raise KernelError(f"attention: cache of shape {tuple(cache.shape)} / {cache.dtype} does not match the heads")
     _per_head(slopes, n_q_heads, "slopes")
     _per_head(sinks, n_q_heads, "sinks")
+    _per_head(head_bias, n_q_heads, "the bias per head")
     r1, r2 = log_bias if log_bias is not None else (None, None)
     _per_head(r1, n_q_heads, "the logarithmic bias")
     _per_head(r2, n_q_heads, "the logarithmic bias")
     if gate is not None and (gate.shape != (n, n_q_heads) or gate.stride(1) != 1 or gate.dtype != q.dtype):
         raise KernelError("attention: the gate must be [n, heads] of q's dtype")
-    f = _func("attention_generic.cu", "lmsf_attention_generic_masked", _GENERIC_MASKED_ARGS)
+    f = _func("attention_generic.cu", "lmsf_attention_generic_weights", _GENERIC_WEIGHTS_ARGS)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0),
            _i32(block_table, "block_table"), block_table.shape[1], block_size, _i32(token_seq, "token_seq"),
            _i32(positions, "positions"), float(scale), float(softcap or 0.0), _ptr(slopes), int(window or 0), n, n_q_heads,
            n_kv_heads, head_dim, dtype_code(q.dtype), 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
-           int(chunk or 0), _ptr(r1), _ptr(r2), _ptr(sinks), _stream())
+           int(chunk or 0), _ptr(r1), _ptr(r2), _ptr(sinks), int(keep_first or 0), 1 if sigmoid else 0, _ptr(head_bias), _stream())
     _check(rc, "attention_generic.cu", "lmsf_attention_generic")
 
 
@@ -305,6 +333,18 @@ def gated_act(out: torch.Tensor, x: torch.Tensor, act: str = "silu"):
         raise KernelError(f"gated_act: unknown activation {act!r} (known: {', '.join(sorted(ACT_CODES))})")
     f = _func("activation.cu", "lmsf_gated_act", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p])
     rc = f(_ptr(out), _ptr(x), n, d, x.stride(0), ACT_CODES[act], dtype_code(out.dtype), _stream())
+    _check(rc, "activation.cu", "lmsf_activation")
+
+
+def poly_norm(out: torch.Tensor, x: torch.Tensor, coef: torch.Tensor, eps: float):
+    """out[t] = a N(x[t]) + b N(x[t]^2) + c N(x[t]^3) + e with (a, b, c, e) = coef (float32 [4] on the device), powers element
+    by element and N the division of a row by its root mean square (eps inside the root); float32 inside.  x: [n, d] view,
+    out: [n, d] contiguous, one dtype."""
+    n, d = out.shape
+    if x.shape != (n, d) or x.stride(1) != 1 or not out.is_contiguous() or x.dtype != out.dtype:
+        raise KernelError("poly_norm: x and out must be [n, d] of one dtype")
+    f = _func("activation.cu", "lmsf_poly_norm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_float, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(x), n, d, x.stride(0), _f32vec(coef, 4, "coef"), float(eps), dtype_code(out.dtype), _stream())
     _check(rc, "activation.cu", "lmsf_activation")
 
 
@@ -882,6 +922,22 @@ def gated_branches(res: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tens
     _check(rc, "stream_norm.cu", "lmsf_stream_norm")
 
 
+def token_shift(out: torch.Tensor, h: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, positions: torch.Tensor,
+                token_seq: torch.Tensor, cu_q: torch.Tensor, state_slot: torch.Tensor):
+    """out[t] = h[t] + (h[t - 1] - h[t]) * mix; h[t - 1] is zero for a request's first token and comes from `state`
+    (float32 [slots, hidden], which then receives the portion's last row) for a portion's first token."""
+    n, hidden = h.shape
+    if out.shape != h.shape or out.dtype != h.dtype or not (out.is_contiguous() and h.is_contiguous()) or out.data_ptr() == h.data_ptr():
+        raise KernelError("token_shift: out and h must be different contiguous tensors of one shape and dtype")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != hidden or not state.is_contiguous():
+        raise KernelError("token_shift: the state must be contiguous float32 [slots, hidden]")
+    f = _func("stream_norm.cu", "lmsf_token_shift",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(h), _f32vec(mix, hidden, "mix"), _ptr(state), _i32(positions, "positions"),
+           _i32(token_seq, "token_seq"), _i32(cu_q, "cu_q"), _i32(state_slot, "state_slot"), n, hidden, dtype_code(h.dtype), _stream())
+    _check(rc, "stream_norm.cu", "lmsf_stream_norm")
+
+
 def stream_concat(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor):
     """out = [a | b] in out's type: two float32 streams [n, D] side by side, [n, 2 D]."""
     n, hidden = a.shape
@@ -1155,6 +1211,18 @@ def head_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, head_dim: int):
     _check(rc, "latent_cache.cu", "lmsf_latent_cache")
 
 
+def value_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, head_dim: int, value_dim: int):
+    """x[t, h, d] *= sigmoid(gate[t, h, d]) for d < value_dim, in place.  x: [n, heads * head_dim], gate: [n, heads * value_dim]
+    (views, last dimension contiguous)."""
+    n = x.shape[0]
+    if x.shape != (n, heads * head_dim) or gate.shape != (n, heads * value_dim) or x.stride(1) != 1 or gate.stride(1) != 1 or \
+            x.dtype != gate.dtype:
+        raise KernelError("value_gate: x [n, heads * head_dim] and gate [n, heads * value_dim] of one dtype")
+    f = _func("latent_cache.cu", "lmsf_value_gate", [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), n, heads, head_dim, value_dim, dtype_code(x.dtype), _stream())
+    _check(rc, "latent_cache.cu", "lmsf_latent_cache")
+
+
 def attention_shared_kv(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, block_size: int,
                         token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int, n_q_heads: int,
                         head_dim: int, gate: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None):
@@ -1267,6 +1335,22 @@ def moe_topk_sigmoid(ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor,
     _check(rc, "moe.cu", "lmsf_moe")
 
 
+def moe_topk_softmax_all(ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor, correction: Optional[torch.Tensor],
+                         outputs: int, weight_scale: float = 1.0):
+    """ids, wts [n, top]: scores s = softmax(logits[t, :outputs]) over all router outputs; the `top` largest s + correction;
+    the weights are the chosen s times weight_scale, not renormalised."""
+    n, top = ids.shape
+    if logits.dtype != torch.float32 or logits.shape[0] != n or logits.shape[1] < outputs or logits.stride(1) != 1:
+        raise KernelError("moe: the router's logits must be float32 [n, >= outputs]")
+    if wts.dtype != torch.float32 or wts.shape != ids.shape or not wts.is_contiguous():
+        raise KernelError("moe: one float32 weight per choice")
+    f = _func("moe.cu", "lmsf_moe_topk_softmax_all",
+              [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
+    rc = f(_ptr(logits), logits.stride(0), _f32vec(correction, outputs, "correction"), n, outputs, top, float(weight_scale),
+           _i32(ids, "ids"), _ptr(wts), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")
+
+
 def moe_align(ids: torch.Tensor, experts: int, tile_rows: int, offsets: torch.Tensor, pair_row: torch.Tensor,
               row_token: torch.Tensor, tiles: torch.Tensor, meta: torch.Tensor):
     """Sorts the (token, choice) pairs by expert on the device: offsets [experts + 1], pair_row [n, top] (row of each
@@ -1294,9 +1378,11 @@ def moe_grouped(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gather: Opt
 
 
 def moe_combine(out: torch.Tensor, down: torch.Tensor, pair_row: torch.Tensor, wts: Optional[torch.Tensor],
-                shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None):
+                shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                identity: Optional[Tuple[torch.Tensor, int, torch.Tensor]] = None):
     """out[t] = sum_j wts[t, j] * down[pair_row[t, j]] + sigmoid(gate[t]) * shared[t].  down: float32 [pairs, width];
-    gate: float32 [n] view (any stride); shared: [n, width] of out's dtype.  wts None: every weight is 1."""
+    gate: float32 [n] view (any stride); shared: [n, width] of out's dtype.  wts None: every weight is 1.  identity (ids [n,
+    top], experts, x [n, width] of out's dtype): a choice numbered `experts` or more adds wts[t, j] * x[t] instead."""
     n, width = out.shape
     top = pair_row.shape[1]
     if wts is not None and (wts.dtype != torch.float32 or tuple(wts.shape) != (n, top) or not wts.is_contiguous()):
@@ -1307,10 +1393,15 @@ def moe_combine(out: torch.Tensor, down: torch.Tensor, pair_row: torch.Tensor, w
         raise KernelError("moe: the shared expert's output must be like out")
     if gate is not None and (gate.dtype != torch.float32 or gate.dim() != 1 or gate.shape[0] != n):
         raise KernelError("moe: one float32 gate value per token")
-    f = _func("moe.cu", "lmsf_moe_combine",
-              [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    ids, experts, x = identity if identity is not None else (None, 0, None)
+    if identity is not None and (tuple(ids.shape) != (n, top) or x.shape != out.shape or x.dtype != out.dtype or not x.is_contiguous()):
+        raise KernelError("moe: experts that return their input need the choices [n, top] and the input, like out")
+    f = _func("moe.cu", "lmsf_moe_combine_identity",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p,
+               c_int, c_void_p, c_void_p])
     rc = f(_ptr(out), _ptr(down), _i32(pair_row, "pair_row"), _ptr(wts), top, _ptr(shared), _ptr(gate),
-           gate.stride(0) if gate is not None else 0, n, width, dtype_code(out.dtype), _stream())
+           gate.stride(0) if gate is not None else 0, n, width, dtype_code(out.dtype), _i32(ids, "ids"), int(experts), _ptr(x),
+           _stream())
     _check(rc, "moe.cu", "lmsf_moe")
 
 

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them."""
-from . import bedenex, llama, redarax, vufolorn  # noqa: F401
+from . import bedenex, llama, redarax, vufolorn, zonidra  # noqa: F401

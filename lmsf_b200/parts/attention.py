@@ -39,7 +39,9 @@ class PagedAttention(Mixer):
                  scale: Optional[float] = None, bias: bool = False, softcap: Optional[float] = None,
                  value_dim: Optional[int] = None, qk_norm: bool = False, qk_norm_eps: float = 1e-6,
                  qk_norm_weights: bool = True, value_norm: bool = False, chunk: Optional[int] = None,
-                 head_gate: bool = False):
+                 head_gate: bool = False, keep_first: int = 0, score_weights: str = "softmax", head_bias: bool = False,
+                 value_gate: bool = False, own_kv: bool = True, cache_window="own",
+                 cache_keep_first: Optional[int] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads cannot be grouped over {num_kv_heads} kv heads")
         # head_dim is the stored size of a query or key head, value_dim that of a value head (default: the same).  The
@@ -69,6 +71,27 @@ class PagedAttention(Mixer):
         self.head_gate = bool(head_gate)
         if self.head_gate and bias:
             raise ValueError("a gate per head with projection biases is not built")
+        # keep_first n (with a window): the request's first n keys stay visible when the window has passed them, at their
+        # true positions.  score_weights "sigmoid": a visible key's weight is sigmoid(score) and the weights are not
+        # normalised over the keys (no softmax).  head_bias: a learned number per query head (weight `head_bias`) added to
+        # every scaled score.  value_gate: the concatenated value heads are multiplied element by element by sigmoid(Wg x)
+        # before the output projection; Wg's rows ride behind q, k, v in the merged matrix.
+        self.keep_first = int(keep_first or 0) if window else 0
+        if score_weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"score weights {score_weights!r} are not supported (known: softmax, sigmoid)")
+        self.sigmoid_weights = score_weights == "sigmoid"
+        self.has_head_bias, self.value_gate = bool(head_bias), bool(value_gate)
+        # own_kv False: the part has no key and value projections; every call of it reads the cache that another call owns
+        self.own_kv = bool(own_kv)
+        if (self.value_gate or not self.own_kv) and (bias or self.head_gate or qk_norm):
+            raise ValueError("a gate per element, or a part without keys and values of its own, is not built with projection "
+                             "biases, a gate per head or a norm of queries and keys")
+        # what the cache keeps may be more than this part sees: other calls that read this call's cache can have wider masks
+        # ("own": what this part's mask needs; None: every key; a number: a window of that size)
+        self.cache_window = (int(window) if window else None) if cache_window == "own" else (int(cache_window) if cache_window else None)
+        self.cache_keep_first = int(cache_keep_first) if cache_keep_first is not None else self.keep_first
+        self.head_bias: Optional[torch.Tensor] = None
+        self._hb32: Optional[torch.Tensor] = None
         self.q_norm: Optional[torch.Tensor] = None
         self.k_norm: Optional[torch.Tensor] = None
         self._qn32: Optional[torch.Tensor] = None
@@ -89,8 +112,11 @@ class PagedAttention(Mixer):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         H, G, dk, dv, D = self.num_heads, self.num_kv_heads, self.qk_dim, self.value_dim, self.hidden_size
-        specs = {"qkv": WeightSpec([(H * dk, D), (G * dk, D), (G * dv, D)] + ([(H, D)] if self.head_gate else [])),
-                 "o": WeightSpec([(D, H * dv)])}
+        merged = [(H * dk, D)] + ([(G * dk, D), (G * dv, D)] if self.own_kv else [])
+        merged += ([(H, D)] if self.head_gate else []) + ([(H * dv, D)] if self.value_gate else [])
+        specs = {"qkv": WeightSpec(merged), "o": WeightSpec([(D, H * dv)])}
+        if self.has_head_bias:
+            specs["head_bias"] = WeightSpec([(H,)], keep_fp32=True)
         if self.has_bias:
             specs["qkv_bias"] = WeightSpec([(H * dk,), (G * dk,), (G * dv,)])
             specs["o_bias"] = WeightSpec([(D,)])
@@ -111,26 +137,30 @@ class PagedAttention(Mixer):
                 return out.reshape(heads * hd, *t.shape[2:])
 
             for name in ("qkv", "qkv_bias"):
-                if name in tensors:
+                if name in tensors and not self.own_kv:
+                    t = tensors[name]
+                    tensors[name] = torch.cat([pad_heads(t[:H * dk], H, dk), t[H * dk:]], 0).contiguous()
+                elif name in tensors:
                     t = tensors[name]
                     q, k, v = t[:H * dk], t[H * dk:(H + G) * dk], t[(H + G) * dk:(H + G) * dk + G * dv]
-                    rest = t[(H + G) * dk + G * dv:]            # the rows of a gate per head, if any
+                    rest = t[(H + G) * dk + G * dv:]            # the rows of a gate, if any
                     tensors[name] = torch.cat([pad_heads(q, H, dk), pad_heads(k, G, dk), pad_heads(v, G, dv), rest], 0).contiguous()
             if "o" in tensors:
                 o = tensors["o"].reshape(-1, H, dv)
                 po = o.new_zeros((o.shape[0], H, hd))
                 po[:, :, :dv] = o
                 tensors["o"] = po.reshape(o.shape[0], H * hd).contiguous()
-        if self.head_gate and H % 8 and "qkv" in tensors:
+        if (self.head_gate or self.value_gate) and "qkv" in tensors and tensors["qkv"].shape[0] % 8:
             # the gate's rows end the merged matrix: zero rows after them keep the product's row stride a multiple of 16
             # bytes, which the attention kernels ask of the queries they read in place
             tensors = dict(tensors)
             t = tensors["qkv"]
-            tensors["qkv"] = torch.cat([t, t.new_zeros((8 - H % 8, t.shape[1]))], 0).contiguous()
+            tensors["qkv"] = torch.cat([t, t.new_zeros((8 - t.shape[0] % 8, t.shape[1]))], 0).contiguous()
         super().set_weights(tensors)
 
     def cache_spec(self) -> Optional[KVCacheSpec]:
-        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.cache_window,
+                           keep_first=self.cache_keep_first if self.cache_window else 0)
 
     def activation_width(self) -> int:
         return 2 * self.q_size + 2 * self.kv_size           # q, k, v and the attention's output
@@ -140,6 +170,8 @@ class PagedAttention(Mixer):
             self.position_encoding.prepare(dtype, device)
         if self.qk_norm and self.qk_norm_weights:
             self._qn32, self._kn32 = self.q_norm.float().contiguous(), self.k_norm.float().contiguous()
+        if self.has_head_bias:
+            self._hb32 = self.head_bias.float().contiguous()
         if dtype == torch.bfloat16 and not kernels.mma_attention_supported(dtype, self.head_dim):
             # right but slow: said once, so that nobody wonders where the time goes
             warnings.warn(f"head_dim {self.head_dim} is beyond the tensor-core attention kernels "
@@ -163,7 +195,11 @@ class PagedAttention(Mixer):
         group = ctx.groups[cache.group]
         fused = self.position_encoding.fused_rotary() if self.position_encoding is not None else None
         hx = h.x if isinstance(h, Prenormed) else h
-        if (FUSE_QKV_ROPE and cache.owner and linear.USE_SKINNY and self.qkv_bias is None and not self.qk_norm and (fused is not None or self.position_encoding is None)
+        if not cache.owner and self.own_kv is False and cache.kv is None:
+            raise ValueError("a part without keys and values of its own was given no cache to read")
+        if cache.owner and not self.own_kv:
+            raise ValueError("a part without key and value projections cannot own a cache: its call must name the call whose cache it reads")
+        if (FUSE_QKV_ROPE and cache.owner and not self.value_gate and linear.USE_SKINNY and self.qkv_bias is None and not self.qk_norm and (fused is not None or self.position_encoding is None)
                 and kernels.gemm_skinny_qkv_rope_supported(hx, self.qkv, self.head_dim, fused[1] if fused else 0,
                                                            fused[2] if fused else True)):
             # a few single tokens (a decode step): projection, rotation and cache write in one kernel
@@ -176,7 +212,8 @@ class PagedAttention(Mixer):
             out = torch.empty((ctx.n_tokens, self.q_size), dtype=hx.dtype, device=hx.device)
             self.attend(ctx, out, q, cache.kv, group)
             return self._project_out(out, then)
-        gate = None
+        gate = vgate = None
+        n_vg = self.num_heads * self.value_dim
         if cache.owner:
             qkv = matmul_tn(h, self.qkv, bias=self.qkv_bias)
             q = qkv[:, :self.q_size]
@@ -184,6 +221,17 @@ class PagedAttention(Mixer):
             v = qkv[:, self.q_size + self.kv_size:self.q_size + 2 * self.kv_size]
             if self.head_gate:
                 gate = qkv[:, self.q_size + 2 * self.kv_size:self.q_size + 2 * self.kv_size + self.num_heads]
+            if self.value_gate:
+                vgate = qkv[:, self.q_size + 2 * self.kv_size:self.q_size + 2 * self.kv_size + n_vg]
+        elif not self.own_kv:   # queries (and the gate) in one product: the matrix holds nothing else
+            qg = matmul_tn(h, self.qkv)
+            q, k, v = qg[:, :self.q_size], None, None
+            if self.value_gate:
+                vgate = qg[:, self.q_size:self.q_size + n_vg]
+        elif self.value_gate:   # the keys and values are another call's although this part has projections for them
+            q = matmul_tn(h, self.qkv[:self.q_size])
+            k = v = None
+            vgate = matmul_tn(h, self.qkv[self.q_size + 2 * self.kv_size:])[:, :n_vg]
         else:  # keys and values are another call's: only the queries are needed
             q = matmul_tn(h, self.qkv[:self.q_size], bias=None if self.qkv_bias is None else self.qkv_bias[:self.q_size])
             k = v = None
@@ -207,6 +255,8 @@ class PagedAttention(Mixer):
                                      self.num_kv_heads, self.head_dim, ctx.error_flag)
         out = torch.empty((ctx.n_tokens, self.q_size), dtype=q.dtype, device=q.device)
         self.attend(ctx, out, q, cache.kv, group, gate)
+        if vgate is not None:
+            kernels.value_gate_(out, vgate, self.num_heads, self.head_dim, self.value_dim)
         return self._project_out(out, then)
 
     def _project_out(self, out: torch.Tensor, then: Optional[NormAfter]):
@@ -219,13 +269,15 @@ class PagedAttention(Mixer):
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, gate=None) -> None:
         paged_attend(ctx, out, q, kv, group, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                      scale=self.scale, window=self.window, softcap=self.softcap, slopes=self._slopes(), chunk=self.chunk,
-                     log_bias=self._log_bias(), gate=gate)
+                     log_bias=self._log_bias(), gate=gate, keep_first=self.keep_first, sigmoid=self.sigmoid_weights,
+                     head_bias=self._hb32)
 
 
 def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, *, num_heads: int,
                  num_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None, softcap: float = 0.0,
                  slopes: Optional[torch.Tensor] = None, kv_planes: int = 2, chunk: Optional[int] = None,
-                 log_bias=None, gate: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> None:
+                 log_bias=None, gate: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                 keep_first: int = 0, sigmoid: bool = False, head_bias: Optional[torch.Tensor] = None) -> None:
     """Attention over pages for any mix of tokens.  bfloat16 with a head size up to 256: single tokens go to the
     split-key decode kernel, longer portions to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for
     head sizes 64 and 128, mma.sync otherwise).  Everything else, float32 included, runs on the generic kernel, which is
@@ -233,8 +285,11 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
     kernels only; the caller keeps its own plain kernel for that layout).  chunk: a query sees the keys of its own chunk of
     positions only; log_bias (r1, r2): r1 * log(1 + r2 * distance) is taken off the scores; sinks [heads]: exp(sink) joins
     the softmax's denominator (all three: every kernel); gate [n, heads]: the output of head h is multiplied by
-    sigmoid(gate[:, h]) (the generic kernel itself, a small kernel after the fast ones)."""
-    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and \
+    sigmoid(gate[:, h]) (the generic kernel itself, a small kernel after the fast ones).  keep_first: with a window, the
+    request's first keys stay visible behind it; sigmoid: a key's weight is sigmoid(score), not normalised; head_bias [heads]:
+    added to the scaled scores."""
+    fast_takes = not (keep_first or sigmoid or head_bias is not None)
+    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and fast_takes and \
             not ctx.extras.get("force_generic_attention"):
         extras = dict(chunk=chunk or 0, log_bias=log_bias, sinks=sinks)
         if ctx.n_decode_seqs:
@@ -310,4 +365,5 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
         raise ValueError("the plain attention kernel of keys and values takes a cache of two planes")
     kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
                               scale, window or 0, num_heads, num_kv_heads, head_dim,
-                              softcap=softcap, slopes=slopes, chunk=chunk or 0, log_bias=log_bias, gate=gate, sinks=sinks)
+                              softcap=softcap, slopes=slopes, chunk=chunk or 0, log_bias=log_bias, gate=gate, sinks=sinks,
+                              keep_first=keep_first if window else 0, sigmoid=sigmoid, head_bias=head_bias)

@@ -76,12 +76,14 @@ class WeightSpec:
 @dataclass(frozen=True)
 class KVCacheSpec:
     """What a mixer needs of the paged cache: per token and layer planes * num_kv_heads * head_dim
-    values; window None keeps all keys, window w keeps the last w.  planes 2: keys and values; planes 1: one vector
-    per token and kv head that serves as both (attention over a cached low-rank vector)."""
+    values; window None keeps all keys, window w keeps the last w and, with keep_first n, the request's first n as
+    well.  planes 2: keys and values; planes 1: one vector per token and kv head that serves as both (attention over a
+    cached low-rank vector)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -108,6 +110,8 @@ class LayerCache:
     group: Optional[int] = None                # index into StepContext.groups
     state: Optional[torch.Tensor] = None       # [slots, *StateSpec.shape]
     owner: bool = True                         # False: read another call's cache, write nothing
+    # per-request state of the block's other parts, by role ([slots, *shape] each): what `Block.state_specs()` asked for
+    extra: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 @dataclass
@@ -139,6 +143,7 @@ class StepContext:
     q_tile128_q0: Optional[torch.Tensor] = None
     n_q_tiles128: int = 0
     extras: Dict[str, Any] = field(default_factory=dict)   # per-step scratch that kernels share across layers
+    embedding_state: Optional[torch.Tensor] = None     # [slots, *shape]: what the embedding's `state_spec()` asked for
 
     @property
     def max_q_len(self) -> int:
@@ -257,6 +262,17 @@ class PositionEncoding(Part):
         return None
 
 
+class Shift(Part):
+    """Mixes every token's row with the row of the token before it in the same request, which is the request's state between
+    steps: `state_spec()` says what a slot holds, `forward(ctx, h, state) -> h'` reads and updates it."""
+
+    def state_spec(self) -> StateSpec:
+        raise NotImplementedError
+
+    def forward(self, ctx: "StepContext", h: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Mixer(Part):
     # takes_prenormed: `forward` accepts a `Prenormed` as h.  fuses_norm: `forward` accepts `then=NormAfter(...)` and
     # may return a `Prenormed`.  A part that says neither is always given and asked for plain tensors.
@@ -299,6 +315,11 @@ class Block:
         """(x, res) -> (x, res): x is the branch output not yet added, res the float32 residual sum."""
         raise NotImplementedError
 
+    def state_specs(self) -> Dict[str, StateSpec]:
+        """Per-request state of fixed size that parts of the block other than the mixer keep across steps, by role; the
+        tensors arrive in `LayerCache.extra` under the same names."""
+        return {}
+
     def entry(self) -> Optional[Tuple[Norm, Part]]:
         """(the norm that the block's input meets first, the part that reads that norm's output), for the block that
         runs before this one and says `fuses_next_norm`: its `forward` is then called with `next_entry=` this pair
@@ -310,7 +331,7 @@ class Block:
 
 # ----------------------------------------------------------------------------- registries
 
-FAMILIES = ("mixer", "feed_forward", "norm", "position_encoding", "block", "embedding", "linear", "stream_entry")
+FAMILIES = ("mixer", "feed_forward", "norm", "position_encoding", "block", "embedding", "linear", "stream_entry", "shift")
 _REGISTRY: Dict[str, Dict[str, Callable[..., Any]]] = {f: {} for f in FAMILIES}
 
 

@@ -61,15 +61,17 @@ class SandwichNormBlock(Block):
     sum into it is made in float32 from the float32 normed branch (the branch is never rounded before it is added).
     One kernel does what lies between two branches: the post norm of the branch before, the add, and the pre norm of
     the branch after (`kernels.stream_norm`); with `next_entry` it also applies the next block's first norm and
-    hands it over as a `Normed`.  A layer may have no feed-forward."""
-    ROLES = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+    hands it over as a `Normed`.  A layer may have no feed-forward.  With a `mixer_shift` the mixer reads the first norm's
+    output mixed with the row of the token before (a `Shift` part, whose state per request the block declares)."""
+    ROLES = {"mixer_norm": "norm", "mixer_shift": "shift", "mixer": "mixer", "mixer_post_norm": "norm",
              "ffn_norm": "norm", "feed_forward": "feed_forward", "ffn_post_norm": "norm"}
-    OPTIONAL_ROLES = ("ffn_norm", "feed_forward", "ffn_post_norm")
+    OPTIONAL_ROLES = ("mixer_shift", "ffn_norm", "feed_forward", "ffn_post_norm")
     fuses_next_norm = True
 
     def __init__(self, parts: Dict[str, Part]):
         super().__init__(parts)
         self.mixer_norm, self._mixer, self.mixer_post = parts["mixer_norm"], parts["mixer"], parts["mixer_post_norm"]
+        self.mixer_shift = parts.get("mixer_shift")
         self.feed_forward = parts.get("feed_forward")
         self.ffn_norm, self.ffn_post = parts.get("ffn_norm"), parts.get("ffn_post_norm")
         if self.feed_forward is not None and (self.ffn_norm is None or self.ffn_post is None):
@@ -80,6 +82,9 @@ class SandwichNormBlock(Block):
 
     def entry(self) -> Optional[Tuple[Norm, Part]]:
         return self.mixer_norm, self._mixer
+
+    def state_specs(self):
+        return {"mixer_shift": self.mixer_shift.state_spec()} if self.mixer_shift is not None else {}
 
     @staticmethod
     def _between(res: torch.Tensor, branch: torch.Tensor, post, nxt: Optional[Norm]):
@@ -93,6 +98,8 @@ class SandwichNormBlock(Block):
     def forward(self, ctx: StepContext, x, res: Optional[torch.Tensor], cache: LayerCache,
                 next_entry: Optional[Tuple[Norm, Part]] = None):
         h, res = self.mixer_norm.forward_residual(x, res)      # x: None (complete stream), a Normed, or a pending branch
+        if self.mixer_shift is not None:
+            h = self.mixer_shift.forward(ctx, h, cache.extra["mixer_shift"])
         a = self._mixer.forward(ctx, h, cache)
         nxt = next_entry[0] if next_entry is not None and hasattr(next_entry[0], "weight_f32") and \
             not getattr(next_entry[0], "has_layer_scale", False) else None

@@ -69,6 +69,14 @@ class DecoderModel:
         m = self.blocks[self.calls[j].layer].mixer
         return m.state_spec() if m is not None else None
 
+    def call_extra_state_specs(self, j: int):
+        """State that the block's other parts keep per request, by role."""
+        return self.blocks[self.calls[j].layer].state_specs()
+
+    def embedding_state_spec(self) -> Optional[StateSpec]:
+        f = getattr(self.embedding, "state_spec", None)
+        return f() if f is not None else None
+
     def prepare(self, dtype: torch.dtype, device: torch.device) -> None:
         for part, _ in self._owned:
             part.prepare(dtype, device)

@@ -6,7 +6,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels
-from .base import Part, StepContext, WeightSpec, register_part
+from .base import Part, StateSpec, StepContext, WeightSpec, register_part
 
 
 @register_part("embedding", "token_embedding")
@@ -72,3 +72,40 @@ class NormedTokenEmbedding(Part):
         first = torch.empty_like(res) if keep else None
         kernels.embed_norm(res, first, self.weight, ctx.token_ids, self._norm32, self.eps, self.scale, ctx.error_flag)
         return res, first
+
+
+@register_part("embedding", "pair_token_embedding")
+class PairTokenEmbedding(Part):
+    """x[t] = E[id_t] * scale + P[(id_{t-1} * mul_prev + id_t * mul_cur) mod buckets]: beside the token's own row a row of a
+    second table that is chosen by the token and the one before it (a hashed pair); a request's first token takes that table's
+    last row, number `buckets`.  The sum is float32 and IS the float32 residual stream (`emits_stream`).  The token before a
+    portion's first token is state of the request: one int32 per state slot, kept on the device (`state_spec`), so that a
+    token sampled on the device is the next step's token before without the host having seen it."""
+    graph_safe = True
+    emits_stream = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0):
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        if self.buckets <= 0 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError(f"a pair table of {buckets} buckets with the multipliers {mul_prev}, {mul_cur}")
+        self.scale = float(scale)
+        self.weight: Optional[torch.Tensor] = None
+        self.pairs: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"weight": WeightSpec([(self.vocab_size, self.hidden_size)]),
+                "pairs": WeightSpec([(self.buckets + 1, self.hidden_size)])}
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((1,), torch.int32)
+
+    def forward_stream(self, ctx: StepContext, keep: bool = False):
+        """(stream, copy of it or None), both float32 [n_tokens, hidden]."""
+        if ctx.embedding_state is None:
+            raise ValueError("the pair embedding needs its state slots (the step's context has none)")
+        res = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
+        kernels.embedding_pairs(res, self.weight, self.pairs, ctx.token_ids, ctx.positions, ctx.token_seq, ctx.cu_q,
+                                ctx.state_slot, ctx.embedding_state, self.buckets, self.mul_prev, self.mul_cur, self.scale,
+                                ctx.error_flag)
+        return res, (res.clone() if keep else None)

@@ -74,3 +74,39 @@ class GatedMLP(FeedForward):
             if p is not None:
                 return p
         return matmul_tn(m, self.down, bias=self.down_bias)
+
+
+@register_part("feed_forward", "plain_mlp")
+class PlainMLP(FeedForward):
+    """A feed-forward without a gate: act(h Wu^T) Wd^T.  The one activation so far, `poly_norm`, is a polynomial whose powers
+    are each divided by their root mean square over the row of `intermediate_size` values:
+        act(z) = a N(z) + b N(z^2) + c N(z^3) + e,   N(x) = x / sqrt(mean(x^2) + eps)
+    with the four numbers (a, b, c, e) a weight of the part (`act`).  The sums and factors are float32 (csrc/activation.cu)."""
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, eps: float, activation: str = "poly_norm"):
+        if activation != "poly_norm":
+            raise ValueError(f"activation {activation!r} is not supported by the plain feed-forward (known: poly_norm)")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.eps, self.activation = float(eps), activation
+        self.up: Optional[torch.Tensor] = None
+        self.down: Optional[torch.Tensor] = None
+        self.act: Optional[torch.Tensor] = None
+        self._coef: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"up": WeightSpec([(self.intermediate_size, self.hidden_size)]),
+                "down": WeightSpec([(self.hidden_size, self.intermediate_size)]),
+                "act": WeightSpec([(4,)], keep_fp32=True)}
+
+    def prepare(self, dtype, device) -> None:
+        self._coef = self.act.float().contiguous()
+
+    def activation_width(self) -> int:
+        return 2 * self.intermediate_size
+
+    def forward(self, ctx: StepContext, h):
+        z = matmul_tn(h, self.up)
+        m = torch.empty_like(z)
+        kernels.poly_norm(m, z, self._coef, self.eps)
+        return matmul_tn(m, self.down)

@@ -14,6 +14,11 @@ experts without the clamp, expert(h) = (act(gate h) * (up h)) Wdown^T; with `wei
 what the expert reads, out = sum_j expert_(e_j)(w_j h): gate and up are linear in h, so the weight is applied, in float32, to
 their products inside the activation kernel, and the combine adds the experts' outputs unweighted.
 
+`routing="softmax_all"` scores by a softmax over ALL router outputs, chooses by score + correction and weighs by the chosen
+scores themselves times `route_scale`, not renormalised.  With `identity_experts` = n the router has n outputs more than there
+are experts; a token that chooses one of them gets its own input back, times the weight (the combine adds it; such a choice
+costs no product).  A shared expert beside gated experts is gated like them (`shared_up` stacks its gate and up matrices).
+
 All experts' matrices are stacked ([experts, ff, width], [experts, width, ff]).  The routing is sorted on the device
 (csrc/moe.cu): no value comes back to the host, and a step's launches have the same shape whatever the routing is, so
 decode steps can be replayed from CUDA graphs.  The router and the shared expert's gate are rows of one float32 product.
@@ -39,13 +44,18 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_size: int, shared_size: int = 0,
                  activation: str = "relu2", router_bias: bool = True, shared_gate: bool = True,
                  routing: str = "softmax_top", groups: int = 1, group_keep: int = 1, limit: Optional[float] = None,
-                 alpha: float = 1.702, weight_on_input: bool = False):
-        if not (0 < top_k <= num_experts):
+                 alpha: float = 1.702, weight_on_input: bool = False, route_scale: float = 1.0, identity_experts: int = 0):
+        if not (0 < top_k <= num_experts + int(identity_experts or 0)):
             raise ValueError(f"{top_k} choices of {num_experts} experts")
         if activation not in kernels.MOE_ACTS and activation != "clamped_swiglu" and activation not in kernels.GLU_ACTS:
             raise ValueError(f"activation {activation!r} is not supported (known: relu2, clamped_swiglu, silu, gelu_tanh, none)")
-        if routing not in ("softmax_top", "sigmoid_groups", "sigmoid_top"):
-            raise ValueError(f"routing {routing!r} is not supported (known: softmax_top, sigmoid_groups, sigmoid_top)")
+        if routing not in ("softmax_top", "sigmoid_groups", "sigmoid_top", "softmax_all"):
+            raise ValueError(f"routing {routing!r} is not supported (known: softmax_top, sigmoid_groups, sigmoid_top, softmax_all)")
+        self.route_scale, self.identity_experts = float(route_scale), int(identity_experts or 0)
+        if self.identity_experts < 0 or (self.identity_experts and routing != "softmax_all"):
+            raise ValueError("experts that return their input are built for the routing softmax_all")
+        if routing == "softmax_all" and (weight_on_input or top_k > num_experts + self.identity_experts):
+            raise ValueError(f"softmax_all: {top_k} choices of {num_experts + self.identity_experts} outputs, weights on the output")
         if routing == "sigmoid_top":
             routing, groups, group_keep = "sigmoid_groups", 1, 1
         self.routing, self.groups, self.group_keep = routing, int(groups), int(group_keep)
@@ -59,8 +69,8 @@ class RoutedExperts(FeedForward):
             raise ValueError("the routing weight on the expert's input is built for silu and gelu_tanh gated experts")
         if self.clamped and not (limit is not None and limit > 0):
             raise ValueError("the clamped activation needs a positive limit")
-        if self.gated and shared_size:
-            raise ValueError("a shared expert beside gated experts is not built")
+        if self.clamped and shared_size:
+            raise ValueError("a shared expert beside clamped experts is not built")
         self.limit, self.alpha = (float(limit) if limit is not None else None), float(alpha)
         self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.expert_size, self.shared_size = int(expert_size), int(shared_size or 0)
@@ -78,12 +88,14 @@ class RoutedExperts(FeedForward):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, E, F = self.hidden_size, self.num_experts, self.expert_size
         # gated experts: "up" lists, expert by expert, the gate matrix and then the up matrix
+        R = E + self.identity_experts                     # router outputs
         specs = {"up": WeightSpec([(F, D)] * (2 * E if self.gated else E)), "down": WeightSpec([(D, F)] * E),
-                 "router": WeightSpec([(E, D)] + ([(1, D)] if self.has_shared_gate else []))}
+                 "router": WeightSpec([(R, D)] + ([(1, D)] if self.has_shared_gate else []))}
         if self.has_router_bias:
-            specs["router_bias"] = WeightSpec([(E,)], keep_fp32=True)
+            specs["router_bias"] = WeightSpec([(R,)], keep_fp32=True)
         if self.shared_size:
-            specs["shared_up"] = WeightSpec([(self.shared_size, D)])
+            # beside gated experts the shared expert is gated too: its gate matrix, then its up matrix
+            specs["shared_up"] = WeightSpec([(self.shared_size, D)] * (2 if self.gated else 1))
             specs["shared_down"] = WeightSpec([(D, self.shared_size)])
         return specs
 
@@ -99,8 +111,11 @@ class RoutedExperts(FeedForward):
         z = matmul_tn(h, self.router, out_dtype=torch.float32)           # [n, experts (+ 1: the shared expert's gate)]
         ids = torch.empty((n, K), dtype=torch.int32, device=dev)
         wts = torch.empty((n, K), dtype=torch.float32, device=dev)
+        R = E + self.identity_experts
         if self.routing == "sigmoid_groups":
             kernels.moe_topk_sigmoid(ids, wts, z, self._bias32, E, self.groups, self.group_keep)
+        elif self.routing == "softmax_all":
+            kernels.moe_topk_softmax_all(ids, wts, z, self._bias32, R, self.route_scale)
         else:
             kernels.moe_topk(ids, wts, z, self._bias32, E)
         pairs = n * K
@@ -139,10 +154,15 @@ class RoutedExperts(FeedForward):
         shared = None
         if self.shared_size:
             s = matmul_tn(h, self.shared_up)
-            if self.activation == "relu2":
+            if self.gated:
+                s2 = torch.empty((n, self.shared_size), dtype=h.dtype, device=dev)
+                kernels.gated_act(s2, s, self.activation)
+                s = s2
+            elif self.activation == "relu2":
                 kernels.relu2_(s)
             shared = matmul_tn(s, self.shared_down)
         out = torch.empty((n, D), dtype=h.dtype, device=dev)
         # weight_on_input: the weights are inside the experts already
-        kernels.moe_combine(out, d, pair_row, None if self.weight_on_input else wts, shared, z[:, E] if self.has_shared_gate else None)
+        kernels.moe_combine(out, d, pair_row, None if self.weight_on_input else wts, shared, z[:, R] if self.has_shared_gate else None,
+                            identity=(ids, E, h) if self.identity_experts else None)
         return out
