@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   const int token = a.cu_q[seq];
   const int ctx = a.ctx_len[seq];
   const int lo = first_seen(ctx - 1, a.window, a.x.chunk);     // the new token sits at position ctx - 1
+  const int keep = a.x.keep_first;                             // keys below it are seen behind the window too
+  const bool sig = a.x.sigmoid != 0;                           // sigmoid weights: no maximum, no denominator
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g4 = lane >> 2, t4 = lane & 3;
   const int head0 = kvh * a.group + hchunk * 16;               // first query head of this block
@@ -130,20 +132,27 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     for (int h = 0; h < 2; ++h)
       if (g4 + h * 8 < n_heads) { r1[h] = a.x.r1[head0 + g4 + h * 8]; r2[h] = a.x.r2[head0 + g4 + h * 8]; }
   }
+  float hb2[2] = {0.f, 0.f};                                   // the heads' biases on the scores, in base-2 units
+  if (a.x.head_bias) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      if (g4 + h * 8 < n_heads) hb2[h] = a.x.head_bias[head0 + g4 + h * 8] * kLog2e;
+  }
 
   // tiles of 64 keys aligned to absolute positions; this split's share of them
-  const int tile_lo = lo / kDecTile, tile_hi = (ctx + kDecTile - 1) / kDecTile;
-  const int per_split = (tile_hi - tile_lo + n_splits - 1) / n_splits;
-  const int tile_begin = tile_lo + split * per_split;
-  const int tile_end = min(tile_hi, tile_begin + per_split);
+  // (with kept first keys: their tiles come first in the list; tile_begin and tile_end count places in the list)
+  const TileRange tiles = tile_range(lo, ctx, keep, kDecTile);
+  const int per_split = (tiles.n + n_splits - 1) / n_splits;
+  const int tile_begin = split * per_split;
+  const int tile_end = min(tiles.n, tile_begin + per_split);
   const int n_tiles = max(0, tile_end - tile_begin);
 
   // a split beyond the cached head of the table copies its own slice (or, if that is too long, reads the table
   // in global memory)
   int table_off = 0;
   {
-    const int blk0 = (tile_begin * kDecTile) >> a.kv.block_shift;
-    const int blk1 = n_tiles > 0 ? min(a.max_blocks, ((min(ctx, tile_end * kDecTile) - 1) >> a.kv.block_shift) + 1) : 0;
+    const int blk0 = n_tiles > 0 ? (tiles.at(tile_begin) * kDecTile) >> a.kv.block_shift : 0;
+    const int blk1 = n_tiles > 0 ? min(a.max_blocks, ((min(ctx, (tiles.at(tile_end - 1) + 1) * kDecTile) - 1) >> a.kv.block_shift) + 1) : 0;
     __syncthreads();
     if (blk1 <= n_head) {
       table = s_table;
@@ -159,12 +168,12 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
   // first stages: tiles that end before the new token are requested now, the others after the wait
   const int safe_end = (ctx - 1) / kDecTile;                  // tiles below this index hold only older keys
   for (int s = 0; s < S - 1; ++s)
-    if (s < n_tiles && tile_begin + s < safe_end)
-      load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, (tile_begin + s) * kDecTile, lo, ctx, table_off);
+    if (s < n_tiles && tiles.at(tile_begin + s) < safe_end)
+      load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, tiles.at(tile_begin + s) * kDecTile, lo, ctx, table_off, keep);
   pdl_wait();
   for (int s = 0; s < S - 1; ++s) {
-    if (s < n_tiles && tile_begin + s >= safe_end)
-      load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, (tile_begin + s) * kDecTile, lo, ctx, table_off);
+    if (s < n_tiles && tiles.at(tile_begin + s) >= safe_end)
+      load_stage<HD, kDecTile, kDecThreads>(smem_base + s * DSt::kBytes, a.kv, table, kvh, tiles.at(tile_begin + s) * kDecTile, lo, ctx, table_off, keep);
     cp_async_commit();
   }
 
@@ -182,7 +191,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     }
   }
 
-  RowState st{{-INFINITY, -INFINITY}, {0.f, 0.f}};
+  RowState st{{sig ? 0.f : -INFINITY, sig ? 0.f : -INFINITY}, {0.f, 0.f}};   // sigmoid weights: the maximum stays 0
   float o[HD / 8][4];
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -194,13 +203,13 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     {
       const int nxt = i + S - 1;
       if (nxt < n_tiles)
-        load_stage<HD, kDecTile, kDecThreads>(smem_base + (nxt % S) * DSt::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kDecTile, lo, ctx, table_off);
+        load_stage<HD, kDecTile, kDecThreads>(smem_base + (nxt % S) * DSt::kBytes, a.kv, table, kvh, tiles.at(tile_begin + nxt) * kDecTile, lo, ctx, table_off, keep);
       cp_async_commit();
     }
     const uint32_t kbase = smem_base + (i % S) * DSt::kBytes;       // this warp's rows are warp * 16 ..
     const uint32_t vbase = kbase + kDecTile * DSt::kRowBytes;
-    const int key0 = (tile_begin + i) * kDecTile + warp * 16;   // first key of this warp's 16
-    if (key0 >= ctx || key0 + 16 <= lo) continue;                // nothing valid (uniform over the warp)
+    const int key0 = tiles.at(tile_begin + i) * kDecTile + warp * 16;   // first key of this warp's 16
+    if (key0 >= ctx || (key0 + 16 <= lo && key0 >= keep)) continue;     // nothing valid (uniform over the warp)
 
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -218,8 +227,8 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + j * 8 + t4 * 2 + (e & 1);
-        const bool ok = key >= lo && key < ctx;
-        float v = ok ? s[j][e] * sl2 : -INFINITY;
+        const bool ok = (key >= lo || key < keep) && key < ctx;
+        float v = ok ? fmaf(s[j][e], sl2, hb2[e >> 1]) : -INFINITY;
         if (biased && ok) v -= log_distance_bias2(r1[e >> 1], r2[e >> 1], ctx - 1 - key);
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -229,7 +238,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(st.m[h], mx[h]);      // finite: at least one key of the 16 is valid
+      const float m_new = sig ? 0.f : fmaxf(st.m[h], mx[h]);      // finite: at least one key of the 16 is valid
       alpha[h] = exp2f(st.m[h] - m_new);
       st.m[h] = m_new;
       st.l[h] *= alpha[h];
@@ -241,7 +250,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          p[j][e] = exp2f(s[j][e] - st.m[e >> 1]);
+          p[j][e] = sig ? sigmoid2(s[j][e]) : exp2f(s[j][e] - st.m[e >> 1]);
           st.l[e >> 1] += p[j][e];
         }
       pf[0] = pack_bf16(p[0][0], p[0][1]);
@@ -307,6 +316,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
       L += sm_l[w * 16 + row] * f;
       acc += sm_o[(w * R + row) * kOS + d] * f;
     }
+    if (sig) L = 1.f;                       // the weights are not normalised: every part is a plain sum (its log-sum-exp 0)
     const int head = head0 + row;
     if (n_splits == 1) {
       if (a.x.sinks) L += exp2f(a.x.sinks[head] * kLog2e - M);   // M is finite: the new token's own key is seen
@@ -338,6 +348,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
         L += f;
         acc += sm_part[s * kPS + row * HD + d] * f;
       }
+      if (sig) L = 1.f;
       a.out[(size_t)token * a.out_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
     }
     return;
@@ -379,7 +390,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
       if (sink2 != -INFINITY) L += exp2f(sink2 - M);
-      const float inv = 1.0f / L;
+      const float inv = sig ? 1.0f : 1.0f / L;
       for (int s = lane; s < n_splits; s += 32) w[s] *= inv;
     }
     __syncthreads();
@@ -414,6 +425,7 @@ __global__ void __launch_bounds__(32 * W) decode_kernel(DecodeArgs a) {
       L += f;
       acc += __ldcg(a.part_o + (base + s) * HD + d) * f;
     }
+    if (sig) L = 1.f;
     a.out[(size_t)token * a.out_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
   }
 }
@@ -605,7 +617,7 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
                                          int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
                                          int n_q_heads, int head_dim, int n_splits, int block_warps, void* scratch,
                                          int kv_planes, int chunk, const float* r1, const float* r2, const float* sinks,
-                                         void* stream) {
+                                         int keep_first, int sigmoid, const float* head_bias, void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (n_served <= 0) return 0;
@@ -634,7 +646,8 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
   if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0) LMSF_REFUSE("attention_decode: the distance bias takes both constants; chunk >= 0");
-  a.x = ScoreExtras{chunk, r1, r2, sinks};
+  if (sigmoid && sinks) LMSF_REFUSE("attention_decode: sinks belong to a softmax, not to sigmoid weights");
+  a.x = ScoreExtras{chunk, r1, r2, sinks, (window > 0 && keep_first > 0) ? keep_first : 0, sigmoid ? 1 : 0, head_bias};
   a.rows = decode_rows(group);
   if (block_warps != 0 && block_warps != 2 && block_warps != 4)
     LMSF_REFUSE("attention_decode: blocks have 2 or 4 warps, not %d", block_warps);
@@ -714,7 +727,8 @@ LMSF_API int lmsf_attention_decode_items(const void* q, long long q_stride, void
                                          const int* block_table, int max_blocks, const void* items, int capacity,
                                          int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
                                          int n_q_heads, int head_dim, int block_warps, void* scratch, int kv_planes,
-                                         int chunk, const float* r1, const float* r2, const float* sinks, void* stream) {
+                                         int chunk, const float* r1, const float* r2, const float* sinks, int keep_first,
+                                         int sigmoid, const float* head_bias, void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (capacity <= 0) return 0;
@@ -740,7 +754,8 @@ LMSF_API int lmsf_attention_decode_items(const void* q, long long q_stride, void
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = nullptr; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = 1;
   if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0) LMSF_REFUSE("attention_decode: the distance bias takes both constants; chunk >= 0");
-  a.x = ScoreExtras{chunk, r1, r2, sinks};
+  if (sigmoid && sinks) LMSF_REFUSE("attention_decode: sinks belong to a softmax, not to sigmoid weights");
+  a.x = ScoreExtras{chunk, r1, r2, sinks, (window > 0 && keep_first > 0) ? keep_first : 0, sigmoid ? 1 : 0, head_bias};
   a.rows = decode_rows(group);
   a.items = (const int4*)items;
   a.cluster = 0;
@@ -756,7 +771,7 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
                                    int n_q_heads, int head_dim, int n_splits, void* scratch, void* stream) {
   return lmsf_attention_decode_width(q, q_stride, out, out_stride, cache, page_stride, block_size, n_kv_heads, block_table,
                                      max_blocks, seq_ids, n_served, n_seqs_total, cu_q, ctx_len, scale, window, n_q_heads,
-                                     head_dim, n_splits, 0, scratch, 2, 0, nullptr, nullptr, nullptr, stream);
+                                     head_dim, n_splits, 0, scratch, 2, 0, nullptr, nullptr, nullptr, 0, 0, nullptr, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -66,7 +66,25 @@ struct ScoreExtras {
   const float* r1;      // [n_q_heads] with r2: r1 * ln(1 + r2 * (p - key)) is taken off the scaled score
   const float* r2;
   const float* sinks;   // [n_q_heads]: exp(sink) is one more term of the softmax's denominator, without a key or a value
+  int keep_first;       // > 0 (with a window): the request's first keep_first keys stay visible behind the window
+  int sigmoid;          // 1: a visible key's weight is sigmoid(score), not normalised over the keys (no softmax, no sinks)
+  const float* head_bias;   // [n_q_heads]: a number per query head added to every scaled score
 };
+// The key tiles that a block walks when the window's keys [lo, hi) are joined by the kept first keys [0, keep): tiles
+// 0 .. n_first - 1 and then tile_lo .. tile_hi - 1 (n_first = 0 when the window's first tile reaches the kept keys anyway).
+struct TileRange {
+  int n_first, tile_lo, n;
+  __device__ __forceinline__ int at(int i) const { return i < n_first ? i : tile_lo + (i - n_first); }
+};
+__device__ __forceinline__ TileRange tile_range(int lo, int hi, int keep_first, int tile) {
+  TileRange r;
+  r.tile_lo = lo / tile;
+  r.n_first = keep_first > 0 ? min((keep_first + tile - 1) / tile, r.tile_lo) : 0;
+  r.n = r.n_first + max(0, (hi + tile - 1) / tile - r.tile_lo);
+  return r;
+}
+// sigmoid of a score given in base-2 units (x * log2(e)): 1 / (1 + 2^-v); -inf gives 0
+__device__ __forceinline__ float sigmoid2(float v) { return __frcp_rn(1.0f + exp2f(-v)); }
 // the first key that a query at position p sees
 __device__ __forceinline__ int first_seen(int p, int window, int chunk) {
   int lo = window > 0 ? max(0, p - window + 1) : 0;
@@ -100,13 +118,13 @@ template <int HD, int TILE = kTileKeys> struct Stage {
 };
 
 // Issues the copies of keys [key0, key0 + TILE) of kv head `kvh` into the stage at `stage_base`, by a block of THREADS.
-// Keys outside [lo, hi) and keys whose page entry is negative are zero-filled, never read.
+// Keys outside [lo, hi) (and not among the first `keep`) and keys whose page entry is negative are zero-filled, never read.
 // A thread copies one 16-byte column of several CONSECUTIVE rows, so that it looks its page up once per
 // page rather than once per row; a warp's copies of one pass cover whole rows (coalesced).
 // `table` may be a copy of a slice of the request's block table: entry i of it is block i + table_off.
 template <int HD, int TILE = kTileKeys, int THREADS = kThreads>
 __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& kv, const int* __restrict__ table, int kvh,
-                                           int key0, int lo, int hi, int table_off = 0) {
+                                           int key0, int lo, int hi, int table_off = 0, int keep = 0) {
   using S = Stage<HD, TILE>;
   const size_t v_off = (size_t)kv.v_off;
   const size_t head_off = (size_t)kvh * kv.block_size * HD;
@@ -119,7 +137,7 @@ __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& k
 #pragma unroll
     for (int it = 0; it < kRowsPerThread; ++it) {
       const int row = row0 + it, key = key0 + row, slot = key & mask;
-      const bool in_range = key >= lo && key < hi;
+      const bool in_range = (key >= lo || key < keep) && key < hi;
       if (slot == 0) have_page = false;
       if (in_range && !have_page) {
         const int page = table[(key >> kv.block_shift) - table_off];
@@ -141,7 +159,7 @@ __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& k
       const int key = key0 + row;
       const bf16* src = kv.cache;
       int bytes = 0;
-      if (key >= lo && key < hi) {
+      if ((key >= lo || key < keep) && key < hi) {
         const int page = table[(key >> kv.block_shift) - table_off];
         if (page >= 0) {
           src = kv.cache + (size_t)page * kv.page_stride + head_off + (size_t)(key & mask) * HD + c * 8;

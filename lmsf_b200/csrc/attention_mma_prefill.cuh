@@ -46,6 +46,9 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
   }
   const bool biased = a.x.r1 != nullptr;
   const float r1 = biased ? a.x.r1[head] : 0.f, r2 = biased ? a.x.r2[head] : 0.f;
+  const int keep = a.x.keep_first;                               // keys below it are seen behind the window too
+  const bool sig = a.x.sigmoid != 0;
+  const float hb2 = a.x.head_bias ? a.x.head_bias[head] * kLog2e : 0.f;
   const int warp_last_pos = start + q0 + min(warp * 16 + 15, rows_valid - 1);
   const int warp_first_pos = start + q0 + min(warp * 16, rows_valid - 1);
   const int warp_lo = first_seen(warp_first_pos, a.window, a.x.chunk);
@@ -61,15 +64,16 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
                                   a.q + (size_t)(tok0 + q0 + row) * a.q_stride + (size_t)head * HD + col) : 0u;
     }
 
-  const int tile_begin = lo / kTileKeys, tile_end = (hi + kTileKeys - 1) / kTileKeys;
-  const int n_tiles = tile_end - tile_begin;
+  const TileRange tiles = tile_range(lo, hi, keep, kTileKeys);
+  const int n_tiles = tiles.n;
   const uint32_t smem_base = smem_u32(smem);
   for (int s = 0; s < kStages - 1; ++s) {
-    if (s < n_tiles) load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, (tile_begin + s) * kTileKeys, lo, hi);
+    if (s < n_tiles) load_stage<HD>(smem_base + s * St::kBytes, a.kv, table, kvh, tiles.at(s) * kTileKeys, lo, hi, 0, keep);
     cp_async_commit();
   }
 
-  RowState st{{-INFINITY, -INFINITY}, {0.f, 0.f}};
+  // sigmoid weights: the running maximum stays 0 and nothing is ever rescaled
+  RowState st{{sig ? 0.f : -INFINITY, sig ? 0.f : -INFINITY}, {0.f, 0.f}};
   float o[HD / 8][4];
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -81,11 +85,11 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
     {
       const int nxt = i + kStages - 1;
       if (nxt < n_tiles)
-        load_stage<HD>(smem_base + (nxt % kStages) * St::kBytes, a.kv, table, kvh, (tile_begin + nxt) * kTileKeys, lo, hi);
+        load_stage<HD>(smem_base + (nxt % kStages) * St::kBytes, a.kv, table, kvh, tiles.at(nxt) * kTileKeys, lo, hi, 0, keep);
       cp_async_commit();
     }
-    const int key0 = (tile_begin + i) * kTileKeys;
-    if (key0 > warp_last_pos || key0 + kTileKeys <= warp_lo) continue;   // all masked for this warp
+    const int key0 = tiles.at(i) * kTileKeys;
+    if (key0 > warp_last_pos || (key0 + kTileKeys <= warp_lo && key0 >= keep)) continue;   // all masked for this warp
     const uint32_t kbase = smem_base + (i % kStages) * St::kBytes;
     const uint32_t vbase = kbase + kTileKeys * St::kRowBytes;
 
@@ -111,8 +115,8 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + j * 8 + t4 * 2 + (e & 1), h = e >> 1;
-        const bool ok = key <= pos[h] && key >= row_lo[h];
-        float v = ok ? s[j][e] * sl2 : -INFINITY;
+        const bool ok = key <= pos[h] && (key >= row_lo[h] || key < keep);
+        float v = ok ? fmaf(s[j][e], sl2, hb2) : -INFINITY;
         if (biased && ok) v -= log_distance_bias2f(r1, r2, dist0[h] - (float)(j * 8 + (e & 1)));
         s[j][e] = v;
         mx[h] = fmaxf(mx[h], v);
@@ -122,7 +126,7 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(st.m[h], mx[h]);
+      const float m_new = sig ? 0.f : fmaxf(st.m[h], mx[h]);
       m_use[h] = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet
       alpha[h] = exp2f(st.m[h] - m_use[h]);
       st.m[h] = m_new;
@@ -132,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
     for (int j = 0; j < 8; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        s[j][e] = exp2f(s[j][e] - m_use[e >> 1]);
+        s[j][e] = sig ? sigmoid2(s[j][e]) : exp2f(s[j][e] - m_use[e >> 1]);
         st.l[e >> 1] += s[j][e];
       }
 #pragma unroll
@@ -170,7 +174,7 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(PrefillArgs a) {
   for (int h = 0; h < 2; ++h) {
     if (!row_ok[h]) continue;
     const int row = warp * 16 + g4 + h * 8;
-    const float inv = 1.0f / st.l[h];
+    const float inv = sig ? 1.0f : 1.0f / st.l[h];
     bf16* dst = a.out + (size_t)(tok0 + q0 + row) * a.out_stride + (size_t)head * HD + t4 * 2;
 #pragma unroll
     for (int nn = 0; nn < HD / 8; ++nn)
@@ -187,7 +191,8 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
                                     const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                     int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
                                     int n_q_heads, int head_dim, int kv_planes, int chunk, const float* r1,
-                                    const float* r2, const float* sinks, void* stream) {
+                                    const float* r2, const float* sinks, int keep_first, int sigmoid,
+                                    const float* head_bias, void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (n_tiles <= 0) return 0;
@@ -204,7 +209,8 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;
   a.group = n_q_heads / n_kv_heads;
   if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0) LMSF_REFUSE("attention_prefill: the distance bias takes both constants; chunk >= 0");
-  a.x = ScoreExtras{chunk, r1, r2, sinks};
+  if (sigmoid && sinks) LMSF_REFUSE("attention_prefill: sinks belong to a softmax, not to sigmoid weights");
+  a.x = ScoreExtras{chunk, r1, r2, sinks, (window > 0 && keep_first > 0) ? keep_first : 0, sigmoid ? 1 : 0, head_bias};
   const int smem = kStages * St::kBytes;
   static bool configured = false;
   if (!configured) {

@@ -97,6 +97,11 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 }
 // Registers move between warpgroups after the launch: the softmax warps hold a row of 128 scores each.
 constexpr int kRegsSoftmax = 224, kRegsOther = 56;
+__device__ __forceinline__ float rcp_approx(float x) {      // 1 / x, 0 for +inf
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float ex2_approx(float x) {      // 2^x, 0 for -inf
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -133,7 +138,7 @@ constexpr int kThreadsTotal = 384;     // three warpgroups; warp 11 only gives i
 // [key0, key0 + 128) of kv head kvh into a tile: [64-wide block of the head][key][128 bytes], 16-byte chunk c of
 // a row at chunk c ^ (key & 7).  Keys outside [lo, hi) or without a page are zero-filled.
 __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv, const int* __restrict__ table, int max_blocks,
-                                            int kvh, bool is_v, int key0, int lo, int hi, int lane) {
+                                            int kvh, bool is_v, int key0, int lo, int hi, int keep, int lane) {
   constexpr int kChunks = HD / 8;
   constexpr int kRowsPerPass = 32 / kChunks;
   const size_t head_off = (is_v ? (size_t)kv.v_off : 0) + (size_t)kvh * kv.block_size * HD;
@@ -143,7 +148,7 @@ __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv
 #pragma unroll 4
   for (int p = 0; p < BN / kRowsPerPass; ++p) {
     const int row = p * kRowsPerPass + r0, key = key0 + row, blk = key >> kv.block_shift;
-    const int page = (key >= lo && key < hi && blk < max_blocks) ? table[blk] : -1;
+    const int page = ((key >= lo || key < keep) && key < hi && blk < max_blocks) ? table[blk] : -1;
     const bool ok = page >= 0;
     const bf16* src = ok ? kv.cache + (size_t)page * kv.page_stride + head_off + (size_t)(key & mask) * HD + c * 8 : kv.cache;
     cp_async_16(dst_tile + col + row * 128 + (((c & 7) ^ (row & 7)) << 4), src, ok ? 16 : 0);
@@ -161,11 +166,16 @@ struct UnitMap {
   int full_pairs, n_kv, units_full_per_tile, n_full, n_units;
   const unsigned short* lead;       // the tiles that lead a pair, in the order of the caller's list
 };
-struct Item { int head, q0, rows, hi, lo, tb, te; };   // a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te)
+// a head and 128 query tokens; it sees the keys [lo, hi) in the tiles [tb, te) and, where a window keeps the request's
+// first keys visible, those in the tiles [0, kf) before them (kf <= tb)
+struct Item { int head, q0, rows, hi, lo, tb, te, kf; };
 struct Unit {
   int seq, kvh, head0, q0, tok0, n, start;
   bool two_heads, two, empty;
   int lo, hi, tile_begin, n_tiles;           // what either item sees
+  // the unit's tiles are 0 .. n_first - 1 (kept first keys behind the window) and then tile_begin ..; place j of that list
+  int n_first;
+  __device__ __forceinline__ int phys(int j) const { return j < n_first ? j : tile_begin + (j - n_first); }
   __device__ __forceinline__ Item item(const Args& a, int x) const {
     Item i;
     i.head = head0 + (two_heads ? x : 0);
@@ -175,6 +185,7 @@ struct Unit {
     i.lo = first_seen(start + i.q0, a.window, a.x.chunk);       // the first row's: later rows start no earlier
     i.tb = i.lo / BN;
     i.te = (i.hi + BN - 1) / BN;
+    i.kf = a.x.keep_first > 0 ? min((a.x.keep_first + BN - 1) / BN, i.tb) : 0;
     return i;
   }
   // kLeft: the kernel is built twice, for even groups of heads (no unit of a head that is left over: the plain
@@ -207,7 +218,8 @@ struct Unit {
     lo = i0.lo;                                                 // the second item is never behind the first
     hi = two ? i1.hi : i0.hi;
     tile_begin = i0.tb;
-    n_tiles = (two ? i1.te : i0.te) - tile_begin;
+    n_first = i0.kf;                                            // (the second item's kept tiles are among these or in its partner's window)
+    n_tiles = n_first + (two ? i1.te : i0.te) - tile_begin;
     empty = empty || n_tiles <= 0;
   }
 };
@@ -225,7 +237,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
   __shared__ int n_lead_mem;
   // What the softmax warps of item x need to know of its next unit, written by the producer of the queries before it
   // announces the unit's queries on q_full[x]; two slots per item, used in turn.
-  struct __align__(16) UnitNote { int head, q0, rows, tb, te, start, tok0, tile_begin, lo, hi, tiles_before, last; };
+  struct __align__(16) UnitNote { int head, q0, rows, tb, te, start, tok0, tile_begin, lo, hi, tiles_before, last, kf, n_first; };
   __shared__ UnitNote notes[2][2];
   __shared__ float bias_tbl[8][kBiasEntries];      // per softmax warp: the distance bias of a tile (see the softmax loop)
   volatile int* failed = &failed_mem;
@@ -335,13 +347,13 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         const int n_box = BN / a.rows_box;
         const int head_row = ((is_v && a.kv.v_off != 0) ? a.kv.n_kv_heads : 0) + u.kvh;   // one plane: the key's row is the value's
         auto fetch_page = [&](int t) {
-          const int blk = ((u.tile_begin + t) * BN + lane * a.rows_box) >> a.kv.block_shift;
+          const int blk = (u.phys(t) * BN + lane * a.rows_box) >> a.kv.block_shift;
           return (t < u.n_tiles && lane < n_box && blk < a.max_blocks) ? table[blk] : -1;
         };
         int page = fetch_page(0);
         for (int t = 0; t < u.n_tiles; ++t) {
           const int g = tiles_before + t, s = g % kStages;       // g: the tile counted over all units of the block
-          const int slot0 = ((u.tile_begin + t) * BN + lane * a.rows_box) & (a.kv.block_size - 1);
+          const int slot0 = (u.phys(t) * BN + lane * a.rows_box) & (a.kv.block_size - 1);
           const uint32_t dst = ring + s * kKBytes + lane * a.rows_box * 128;
           if (g >= kStages && !mbar_wait_f(empty(s), (uint32_t)((g / kStages - 1) & 1), failed)) { ok = false; break; }
           const int next_page = fetch_page(t + 1);
@@ -359,7 +371,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         for (int t = 0; t < u.n_tiles; ++t) {
           const int g = tiles_before + t, s = g % kStages;
           if (g >= kStages && !mbar_wait_f(empty(s), (uint32_t)((g / kStages - 1) & 1), failed)) { ok = false; break; }
-          gather_tile(ring + s * kKBytes, a.kv, table, a.max_blocks, u.kvh, is_v, (u.tile_begin + t) * BN, u.lo, u.hi, lane);
+          gather_tile(ring + s * kKBytes, a.kv, table, a.max_blocks, u.kvh, is_v, u.phys(t) * BN, u.lo, u.hi, a.x.keep_first, lane);
           cp_async_arrive(full(s));
         }
       }
@@ -390,8 +402,11 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       if (u.empty) continue;
       const Item it0 = u.item(a, 0), it1 = u.item(a, 1);
       const int nx = u.two ? 2 : 1;
-      const int n_tiles = u.n_tiles, tile_begin = u.tile_begin;
-      auto active = [&](int x, int t) { return x == 0 ? (t >= it0.tb && t < it0.te) : (u.two && t >= it1.tb && t < it1.te); };
+      const int n_tiles = u.n_tiles;
+      // whether item x has tile t (a tile's number among the keys, not its place in the unit's list)
+      auto active = [&](int x, int t) {
+        return x == 0 ? (t < it0.kf || (t >= it0.tb && t < it0.te)) : (u.two && (t < it1.kf || (t >= it1.tb && t < it1.te)));
+      };
       // jx: how many tiles item x has had in this unit; j: tile counted from the unit's first
       auto issue_s = [&](int x, int j) {                          // S of item x and tile j
         const uint64_t dq = dq0 + (uint64_t)((x * kQBytes) >> 4);
@@ -403,7 +418,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         }
         umma_commit(leader, s_full(x));
         // the item's last scores of this unit: when they are complete its queries may be overwritten by the next unit's
-        if (tile_begin + j == (x == 0 ? it0.te : it1.te) - 1) umma_commit(leader, q_free(x));
+        if (u.phys(j) == (x == 0 ? it0.te : it1.te) - 1) umma_commit(leader, q_free(x));
       };
       // O of item x += P V of tile j for the keys of half h (64 of the 128), P from tensor memory
       auto issue_pv = [&](int x, int j, int jx, int h) {
@@ -436,7 +451,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       if (ok) {
 #pragma unroll
         for (int x = 0; x < 2; ++x)
-          if (x < nx && active(x, tile_begin)) issue_s(x, 0);
+          if (x < nx && active(x, u.phys(0))) issue_s(x, 0);
         umma_commit(leader, k_empty(tiles_before % kStages));
       }
       // The two items take turns: while one item's softmax runs, the tensor core works on the other item's
@@ -444,8 +459,9 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       // thread are executed in the order of their issue.
       int jx[2] = {0, 0};
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int g = tiles_before + j, s = g % kStages, s1 = (g + 1) % kStages, t = tile_begin + j;
+        const int g = tiles_before + j, s = g % kStages, s1 = (g + 1) % kStages, t = u.phys(j);
         const bool more = j + 1 < n_tiles;
+        const int t_next = more ? u.phys(j + 1) : -1;
         bool v_ready = false;
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
@@ -465,9 +481,9 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
             tc_fence_after();
             issue_pv(x, j, jx[x], 1);
             ++jx[x];
-            if (!active(x, t + 1)) umma_commit(leader, o_done(x));     // the item's last tile
+            if (t == (x == 0 ? it0.te : it1.te) - 1) umma_commit(leader, o_done(x));     // the item's last tile
           }
-          if (more && active(x, t + 1)) {
+          if (more && active(x, t_next)) {
             ok = k_wait(j + 1);
             if (!ok) continue;
             issue_s(x, j + 1);
@@ -478,10 +494,10 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         if (more) umma_commit(leader, k_empty(s1));
       }
       tiles_before += n_tiles;
-      item_tiles_before[0] += it0.te - it0.tb;
+      item_tiles_before[0] += it0.kf + it0.te - it0.tb;
       units_before[0] += 1;
       if (u.two) {
-        item_tiles_before[1] += it1.te - it1.tb;
+        item_tiles_before[1] += it1.kf + it1.te - it1.tb;
         units_before[1] += 1;
       }
     }
@@ -516,7 +532,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
                                     !mbar_wait_f(taken(x), (uint32_t)((units_before[x] - 1) & 1), failed))) { ok = false; break; }
         if (lane == 0) {
           notes[x][units_before[x] & 1] = UnitNote{me.head, me.q0, me.rows, me.tb, me.te, u.start, u.tok0, u.tile_begin, u.lo, u.hi,
-                                                   tiles_before, 0};
+                                                   tiles_before, 0, me.kf, u.n_first};
           mbar_arrive_expect_tx(q_full(x), kQBytes);
 #pragma unroll
           for (int hb = 0; hb < kHB; ++hb)
@@ -559,22 +575,27 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const volatile UnitNote* note = &notes[x][my_units_before & 1];
       if (note->last) break;
       mbar_arrive(taken(x));
-      struct { int rows, tb, te; } me = {note->rows, note->tb, note->te};
+      struct { int rows, tb, te, kf; } me = {note->rows, note->tb, note->te, note->kf};
+      const int u_first = note->n_first, u_tile_begin = note->tile_begin, u_tiles_before = note->tiles_before;
       const int q_pos0 = note->start + note->q0;                    // position of the item's first query
-      const int stage0 = note->tiles_before + me.tb - note->tile_begin;   // the item's first tile counted over the block's units
       const int u_lo = note->lo, u_hi = note->hi;
       const bool row_ok = row < me.rows;
       const int pos = q_pos0 + min(row, me.rows - 1);                // this thread's query position
       const int row_lo = first_seen(pos, a.window, a.x.chunk);
-      float m_run = -INFINITY, l_run = 0.f;
-      const int my_tiles = me.te - me.tb;
+      const int keep = a.x.keep_first;
+      const bool sig = a.x.sigmoid != 0;                             // sigmoid weights: no maximum, no rescaling, no denominator
+      const float hb2 = a.x.head_bias ? a.x.head_bias[note->head] * kLog2e : 0.f;
+      float m_run = sig ? 0.f : -INFINITY, l_run = 0.f;
+      const int my_tiles = me.kf + me.te - me.tb;
       for (int j = 0; j < my_tiles; ++j) {                           // j counts this item's tiles
         // S of the tile is complete, and with it every product issued before it: P V of the tile before too
         ok = mbar_wait_f(s_full(x), (uint32_t)((my_tiles_before + j) & 1), failed);
         if (!ok) break;
         tc_fence_after();
-        const int key0 = (me.tb + j) * BN;
-        const int ju = stage0 + j;                                   // the tile counted over the block's units: its stage
+        const int tile = j < me.kf ? j : me.tb + (j - me.kf);       // the tile's number among the keys
+        const int key0 = tile * BN;
+        // the tile counted over the block's units: its stage
+        const int ju = u_tiles_before + (tile < u_first ? tile : u_first + tile - u_tile_begin);
         // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
         // the test is the same for the whole group of warps.
         // (the item's last row starts latest: a tile that begins before that start has keys some row does not see)
@@ -606,7 +627,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
 #pragma unroll
           for (int i = 0; i < BN; ++i) {
             const int key = key0 + i;
-            if ((key > pos) | (key < row_lo)) sc[i] = -INFINITY;
+            if ((key > pos) | ((key < row_lo) & (key >= keep))) sc[i] = -INFINITY;
           }
         }
         // four chains of three-input maxima: 128 values in 16 dependent steps
@@ -621,9 +642,9 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         }
         float mx = fmaxf(fmax3(mx0, mx1, mx2), fmax3(mx3, sc[BN - 4], sc[BN - 3]));
         mx = fmax3(mx, sc[BN - 2], sc[BN - 1]);
-        mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
+        mx = fmaf(mx, sl2, hb2);                                  // scores enter the exponent as s * scale * log2(e) + the head's bias
         float alpha = 1.f;
-        const bool grow = mx > m_run + kRescaleThreshold;         // also true for the first keys a row sees
+        const bool grow = !sig && mx > m_run + kRescaleThreshold; // also true for the first keys a row sees
         if (grow) {
           alpha = exp2f(m_run - mx);                              // 0 when m_run is -inf
           m_run = mx;
@@ -648,13 +669,13 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
           if (!ok) break;
           for (int idx = row; idx < kHB * BN * 8; idx += kSoftmaxThreads) {
             const int r = (idx >> 3) % BN;
-            if (r < r_lo || r >= r_hi)
+            if ((r < r_lo && key0 + r >= keep) || r >= r_hi)
               asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v + (idx >> 3) * 128 + (idx & 7) * 16), "r"(0) : "memory");
           }
           fence_async_smem();
         }
         // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
-        const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+        const float neg_m = (m_run == -INFINITY ? 0.f : -m_run) + hb2;
         // The scaling, the subtraction of the maximum and the row sums are packed (two values per instruction); the
         // exponentials come from the special-function unit.  (Tried and slower on this kernel: a share of the
         // exponentials by a polynomial on the FMA pipe, and exponentials of bfloat16 pairs; the softmax warps are
@@ -670,8 +691,13 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
             const uint64_t x2 = fma2(pk2(sc[h * 64 + 2 * i], sc[h * 64 + 2 * i + 1]), sl2_2, neg_m2);
             float p0, p1, x0, x1;
             upk2(x2, x0, x1);
-            p0 = ex2_approx(x0);
-            p1 = ex2_approx(x1);
+            if (sig) {                                            // 1 / (1 + 2^-x); a masked score (-inf) gives 0
+              p0 = rcp_approx(1.0f + ex2_approx(-x0));
+              p1 = rcp_approx(1.0f + ex2_approx(-x1));
+            } else {
+              p0 = ex2_approx(x0);
+              p1 = ex2_approx(x1);
+            }
             lsum = add2(lsum, pk2(p0, p1));
             w[i] = pack_bf16(p0, p1);
           }
@@ -693,7 +719,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       if (ok && my_tiles > 0) {
         tc_fence_after();
         if (a.x.sinks) l_run += exp2f(a.x.sinks[note->head] * kLog2e - m_run);   // m_run is finite: a row sees its own key
-        const float inv = 1.0f / l_run;
+        const float inv = sig ? 1.0f : 1.0f / l_run;
         bf16* dst = a.out + (size_t)(note->tok0 + note->q0 + row) * a.out_stride + (size_t)note->head * HD;
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -766,7 +792,8 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
                                        int n_kv_heads, const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                        int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
                                        int n_q_heads, int head_dim, int* error_flag, int kv_planes, int chunk,
-                                       const float* r1, const float* r2, const float* sinks, void* stream) {
+                                       const float* r1, const float* r2, const float* sinks, int keep_first, int sigmoid,
+                                       const float* head_bias, void* stream) {
   using namespace lmsf;
   using namespace lmsf::tc;
   if (n_tiles <= 0) return 0;
@@ -788,7 +815,8 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
   a.group = n_q_heads / n_kv_heads; a.error_flag = error_flag; a.n_q_tiles = n_tiles;
   if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0 || (r1 && !(scale > 0.f)))
     LMSF_REFUSE("attention_prefill_tc: the distance bias takes both constants and a positive scale; chunk >= 0");
-  a.x = ScoreExtras{chunk, r1, r2, sinks};
+  if (sigmoid && sinks) LMSF_REFUSE("attention_prefill_tc: sinks belong to a softmax, not to sigmoid weights");
+  a.x = ScoreExtras{chunk, r1, r2, sinks, (window > 0 && keep_first > 0) ? keep_first : 0, sigmoid ? 1 : 0, head_bias};
   // pages of 8 keys and more come by tensor-map copies (a box of rows_box keys starts on a 1024-byte
   // boundary of the swizzled tile); smaller pages by cp.async
   a.rows_box = block_size < BN ? block_size : BN;

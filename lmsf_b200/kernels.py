@@ -626,18 +626,21 @@ def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, wha
 
 
 
-def _score_extras(n_q_heads: int, chunk, log_bias, sinks):
-    """(chunk, r1, r2, sinks) as the tensor-core attention kernels take them: what a design adds to the causal softmax.
-    chunk > 0: a query at position p sees the keys p - p % chunk .. p only.  log_bias (r1, r2), float32 [n_q_heads] each:
-    r1 * log(1 + r2 * distance) is taken off the scaled scores.  sinks, float32 [n_q_heads]: exp(sink) is one more term
-    of the softmax's denominator."""
+def _score_extras(n_q_heads: int, chunk, log_bias, sinks, keep_first=0, sigmoid=False, head_bias=None):
+    """(chunk, r1, r2, sinks, keep_first, sigmoid, head_bias) as the tensor-core attention kernels take them: what a design
+    adds to the causal softmax.  chunk > 0: a query at position p sees the keys p - p % chunk .. p only.  log_bias (r1, r2),
+    float32 [n_q_heads] each: r1 * log(1 + r2 * distance) is taken off the scaled scores.  sinks, float32 [n_q_heads]:
+    exp(sink) is one more term of the softmax's denominator.  keep_first (with a window): the request's first keys stay
+    visible behind it.  sigmoid: a visible key's weight is sigmoid(score), not normalised.  head_bias, float32 [n_q_heads]:
+    added to the scaled scores."""
+    _per_head(head_bias, n_q_heads, "the bias per head")
     r1, r2 = log_bias if log_bias is not None else (None, None)
     _per_head(r1, n_q_heads, "the logarithmic bias")
     _per_head(r2, n_q_heads, "the logarithmic bias")
     _per_head(sinks, n_q_heads, "sinks")
     if chunk is not None and int(chunk) < 0:
         raise KernelError(f"attention: a chunk of {chunk} positions")
-    return int(chunk or 0), _ptr(r1), _ptr(r2), _ptr(sinks)
+    return int(chunk or 0), _ptr(r1), _ptr(r2), _ptr(sinks), int(keep_first or 0), 1 if sigmoid else 0, _ptr(head_bias)
 
 
 _DECODE_WIDTHS = {}
@@ -732,7 +735,8 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
                      block_size: int, seq_ids: Optional[torch.Tensor], n_served: int, cu_q: torch.Tensor,
                      ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int,
                      head_dim: int, n_splits: int, scratch: Optional[torch.Tensor], warps: int = 0, kv_planes: int = 2,
-                     chunk: int = 0, log_bias=None, sinks: Optional[torch.Tensor] = None):
+                     chunk: int = 0, log_bias=None, sinks: Optional[torch.Tensor] = None, keep_first: int = 0,
+                     sigmoid: bool = False, head_bias: Optional[torch.Tensor] = None):
     """Attention of requests that bring ONE query token each (row cu_q[s] of q), over their ctx_len[s] keys
     in pages.  seq_ids: int32 [n_served] rows of the block table that are served (None: all, in order).
     scratch: float32, at least attention_decode_scratch_floats(...) values when n_splits > 1, all zero when it is
@@ -741,7 +745,7 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
     kv_planes 1: the cache holds one vector per token and kv head that is key and value at once.
     chunk, log_bias, sinks: see _score_extras."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode", kv_planes)
-    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks, keep_first, sigmoid, head_bias)
     n_total = block_table.shape[0]
     need = attention_decode_scratch_floats(n_total, n_q_heads, n_splits, head_dim)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
@@ -752,7 +756,7 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
     f = _func("attention_mma.cu", "lmsf_attention_decode_width",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
                c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
-               c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
+               c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_ids, "seq_ids"), n_served, n_total,
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim,
@@ -790,11 +794,12 @@ def attention_decode_items(out: torch.Tensor, q: torch.Tensor, cache: torch.Tens
                            block_size: int, items: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor,
                            scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int, warps: int,
                            scratch: torch.Tensor, kv_planes: int = 2, chunk: int = 0, log_bias=None,
-                           sinks: Optional[torch.Tensor] = None):
+                           sinks: Optional[torch.Tensor] = None, keep_first: int = 0,
+                           sigmoid: bool = False, head_bias: Optional[torch.Tensor] = None):
     """attention_decode with splits per request, over a list made by decode_build_items.  scratch: float32, at
     least attention_decode_items_scratch_floats(capacity, ...) values, zero when first used."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode_items", kv_planes)
-    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks, keep_first, sigmoid, head_bias)
     need = attention_decode_items_scratch_floats(items.shape[0], n_q_heads, head_dim)
     if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
         raise KernelError(f"attention_decode_items: a list of {items.shape[0]} entries needs {need} float32 values of scratch")
@@ -802,7 +807,7 @@ def attention_decode_items(out: torch.Tensor, q: torch.Tensor, cache: torch.Tens
     f = _func("attention_mma.cu", "lmsf_attention_decode_items",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
                c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int,
-               c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
+               c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _ptr(items), items.shape[0], block_table.shape[0],
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim, int(warps),
@@ -813,16 +818,17 @@ def attention_decode_items(out: torch.Tensor, q: torch.Tensor, cache: torch.Tens
 def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                       ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                      kv_planes: int = 2, chunk: int = 0, log_bias=None, sinks: Optional[torch.Tensor] = None):
+                      kv_planes: int = 2, chunk: int = 0, log_bias=None, sinks: Optional[torch.Tensor] = None, keep_first: int = 0,
+                      sigmoid: bool = False, head_bias: Optional[torch.Tensor] = None):
     """Attention of prompt portions.  Tile i covers the query tokens tile_q0[i] .. tile_q0[i] + 63 (counted
     inside the portion) of request tile_seq[i]."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill", kv_planes)
-    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks, keep_first, sigmoid, head_bias)
     d = _mma_defines(head_dim)
     f = _func("attention_mma.cu", "lmsf_attention_prefill",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
                c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int,
-               c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
+               c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
@@ -844,16 +850,17 @@ def attention_prefill_tc(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor
                          block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                          ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
                          error_flag: Optional[torch.Tensor] = None, kv_planes: int = 2, chunk: int = 0, log_bias=None,
-                         sinks: Optional[torch.Tensor] = None):
+                         sinks: Optional[torch.Tensor] = None, keep_first: int = 0,
+                         sigmoid: bool = False, head_bias: Optional[torch.Tensor] = None):
     """Attention of prompt portions on tcgen05 tensor cores (head size 64 or 128).  Tile i covers the query
     tokens tile_q0[i] .. tile_q0[i] + 127 (counted inside the portion) of request tile_seq[i]."""
     _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill_tc", kv_planes)
-    extras = _score_extras(n_q_heads, chunk, log_bias, sinks)
+    extras = _score_extras(n_q_heads, chunk, log_bias, sinks, keep_first, sigmoid, head_bias)
     d = _mma_defines(head_dim)[:1]
     f = _func("attention_tc.cu", "lmsf_attention_prefill_tc",
               [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_int, c_int,
                c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p,
-               c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], d)
+               c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], block_size,
            n_kv_heads, _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),

@@ -288,15 +288,15 @@ def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch
     sigmoid(gate[:, h]) (the generic kernel itself, a small kernel after the fast ones).  keep_first: with a window, the
     request's first keys stay visible behind it; sigmoid: a key's weight is sigmoid(score), not normalised; head_bias [heads]:
     added to the scaled scores."""
-    fast_takes = not (keep_first or sigmoid or head_bias is not None)
-    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and fast_takes and \
+    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and \
             not ctx.extras.get("force_generic_attention"):
-        extras = dict(chunk=chunk or 0, log_bias=log_bias, sinks=sinks)
+        extras = dict(chunk=chunk or 0, log_bias=log_bias, sinks=sinks, keep_first=keep_first if window else 0,
+                      sigmoid=sigmoid, head_bias=head_bias)
         if ctx.n_decode_seqs:
             max_ctx = ctx.extras.get("decode_max_ctx")
             if max_ctx is None:
                 max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
-            visible = min(max_ctx, window) if window else max_ctx
+            visible = min(max_ctx, window + (keep_first or 0)) if window else max_ctx
             if chunk:
                 visible = min(visible, chunk)
             # the mean matters to the plan only where it is far below the longest context (a graph names its class)
