@@ -173,3 +173,63 @@ def forward(cfg, W, tokens, dtype=torch.float64, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return rms_norm(x, W["final.norm"], eps) @ W["head"].T
+
+
+# ----------------------------------------------------------------------------- tensors of a configuration
+
+def tensor_shapes(cfg):
+    """{name: shape} of every tensor that a model of this configuration stores, from the configuration alone."""
+    D, V = cfg["width"], cfg["vocab"]
+    out = {"embed": (V, D), "final.norm": (D,), "head": (V, D)}
+    b = cfg["embedding"].get("bigram")
+    if b:
+        out["bigram"] = (b["buckets"] + 1, D)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        out.update({p + "norm1": (D,), p + "norm1b": (D,), p + "ls1": (D,), p + "shift": (D,), p + "mix.q": (H * dk, D),
+                    p + "mix.pb": (H,), p + "mix.g": (H * dv, D), p + "mix.o": (D, H * dv)})
+        if m.get("kv_from") is None:
+            out.update({p + "mix.k": (G * dk, D), p + "mix.v": (G * dv, D)})
+        f = L.get("mlp")
+        if f is None:
+            continue
+        out.update({p + "norm2": (D,), p + "norm2b": (D,), p + "ls2": (D,)})
+        if f["kind"] == "dense":
+            out.update({p + "mlp.up": (f["ff"], D), p + "mlp.down": (D, f["ff"]), p + "mlp.act": (4,)})
+        else:
+            r, F = f["router"], f["expert"]["ff"]
+            R = r["experts"] + r.get("identity", 0)
+            out.update({p + "mlp.router": (R, D), p + "mlp.correction": (R,)})
+            for e in range(r["experts"]):
+                out.update({p + f"mlp.e{e}.gate": (F, D), p + f"mlp.e{e}.up": (F, D), p + f"mlp.e{e}.down": (D, F)})
+            if f.get("shared"):
+                S = f["shared"]["ff"]
+                out.update({p + "mlp.shared.gate": (S, D), p + "mlp.shared.up": (S, D), p + "mlp.shared.down": (D, S),
+                            p + "mlp.shared.sg": (1, D)})
+    return out
+
+
+def random_weights(cfg, seed=0, std=None, dtype=torch.bfloat16):
+    """Weights under which every mechanism moves the result: norm weights and layer scales around 1, shift vectors between 0
+    and 1, biases per head of either sign, polynomial coefficients of order 1, corrections that change some choices."""
+    g = torch.Generator().manual_seed(seed)
+    W = {}
+    for name, shape in tensor_shapes(cfg).items():
+        last = name.split(".")[-1]
+        if last in ("norm1", "norm2", "norm1b", "norm2b", "norm", "ls1", "ls2"):
+            t = 0.6 + 0.8 * torch.rand(shape, generator=g)
+        elif last == "shift":
+            t = torch.rand(shape, generator=g)
+        elif last == "pb":
+            t = torch.randn(shape, generator=g) - 1.0
+        elif last == "act":
+            t = torch.randn(shape, generator=g)
+        elif last == "correction":
+            t = 0.1 * torch.randn(shape, generator=g)
+        elif name in ("embed", "bigram"):
+            t = torch.randn(shape, generator=g) * (std or 0.5)
+        else:
+            t = torch.randn(shape, generator=g) * (std or 1.0 / math.sqrt(shape[-1]))
+        W[name] = t.to(dtype)
+    return W
