@@ -469,17 +469,17 @@ def main() -> int:
     ap.add_argument("--serve", action="store_true",
                     help="instead of the contract's line: 64 requests of 128..2048 prompt tokens and 256 generated "
                          "tokens each through the engine's continuous batching")
-    ap.add_argument("--design", default=None, choices=["vufolorn", "redarax", "bedenex"],
+    ap.add_argument("--design", default=None, choices=["vufolorn", "redarax", "bedenex", "zonidra"],
                     help="instead of the default line: prefill and decode tokens/s of that design at two layer sizes "
                          "beside the engine's closest other model of equal width (vufolorn: the Llama shape; redarax: "
-                         "vufolorn; bedenex: vufolorn and the Llama shape), and its kernels alone against their rooflines")
+                         "vufolorn; bedenex and zonidra: vufolorn and the Llama shape), and its kernels alone against their rooflines")
     a = ap.parse_args()
     if a.design is not None:
         if a.gpus != 1 or a.impl != "ours":
             print("bench.py: --design runs this engine on one GPU")
             return 2
-        from lmsf_b200.benchmarks import bedenex_bench, design_bench, redarax_bench
-        module = {"redarax": redarax_bench, "bedenex": bedenex_bench}.get(a.design, design_bench)
+        from lmsf_b200.benchmarks import bedenex_bench, design_bench, redarax_bench, zonidra_bench
+        module = {"redarax": redarax_bench, "bedenex": bedenex_bench, "zonidra": zonidra_bench}.get(a.design, design_bench)
         return module.run(sys.modules[__name__], a.steps, max(a.warmup, 3), peaks())
     if a.impl == "reference":
         if a.gpus != 1:
