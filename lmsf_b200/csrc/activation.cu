@@ -231,6 +231,43 @@ __global__ void __launch_bounds__(256) poly_norm_kernel(T* __restrict__ out, con
   }
 }
 
+// the same, four values a thread and access: d % 4 == 0, aligned rows
+template <typename T>
+__global__ void __launch_bounds__(512) poly_norm4_kernel(T* __restrict__ out, const T* __restrict__ in, int d, long long in_stride,
+                                                         const float* __restrict__ coef, float eps) {
+  __shared__ float scratch[3][33];
+  const T* row = in + (size_t)blockIdx.x * in_stride;
+  T* o = out + (size_t)blockIdx.x * d;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+    float z[4];
+    ld4(row + i, z);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float z2 = z[k] * z[k];
+      s2 += z2;
+      s4 = fmaf(z2, z2, s4);
+      s6 = fmaf(z2 * z2, z2, s6);
+    }
+  }
+  s2 = block_sum(s2, scratch[0]);
+  s4 = block_sum(s4, scratch[1]);
+  s6 = block_sum(s6, scratch[2]);
+  const float inv = 1.0f / (float)d;
+  const float f1 = coef[0] / sqrtf(fmaf(s2, inv, eps)), f2 = coef[1] / sqrtf(fmaf(s4, inv, eps)),
+              f3 = coef[2] / sqrtf(fmaf(s6, inv, eps)), e = coef[3];
+  for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+    float z[4], r[4];
+    ld4(row + i, z);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float z2 = z[k] * z[k];
+      r[k] = fmaf(f1, z[k], fmaf(f2, z2, fmaf(f3, z2 * z[k], e)));
+    }
+    st4(o + i, r);
+  }
+}
+
 }  // namespace lmsf
 
 // in: [n, d] with in_stride elements between rows; out: [n, d] contiguous; coef: float32 [4] on the device.
@@ -240,6 +277,15 @@ LMSF_API int lmsf_poly_norm(void* out, const void* in, int n, int d, long long i
   if (n <= 0) return 0;
   if (d <= 0 || in_stride < d || !(eps > 0.f)) LMSF_REFUSE("poly_norm: d=%d, in_stride=%lld, eps=%g", d, in_stride, eps);
   cudaStream_t s = (cudaStream_t)stream;
+  const int threads = d >= 4096 ? 512 : 256;
+  if (dtype == LMSF_F32 && rows_take4<float>(in, d, in_stride) && (uintptr_t)out % 16 == 0) {
+    poly_norm4_kernel<float><<<n, threads, 0, s>>>((float*)out, (const float*)in, d, in_stride, coef, eps);
+    return LMSF_LAUNCH_STATUS();
+  }
+  if (dtype == LMSF_BF16 && rows_take4<bf16>(in, d, in_stride) && (uintptr_t)out % 8 == 0) {
+    poly_norm4_kernel<bf16><<<n, threads, 0, s>>>((bf16*)out, (const bf16*)in, d, in_stride, coef, eps);
+    return LMSF_LAUNCH_STATUS();
+  }
   if (dtype == LMSF_F32) poly_norm_kernel<float><<<n, 256, 0, s>>>((float*)out, (const float*)in, d, in_stride, coef, eps);
   else if (dtype == LMSF_BF16) poly_norm_kernel<bf16><<<n, 256, 0, s>>>((bf16*)out, (const bf16*)in, d, in_stride, coef, eps);
   else LMSF_REFUSE("poly_norm: unknown dtype code %d", dtype);

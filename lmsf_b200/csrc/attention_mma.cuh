@@ -83,8 +83,14 @@ __device__ __forceinline__ TileRange tile_range(int lo, int hi, int keep_first, 
   r.n = r.n_first + max(0, (hi + tile - 1) / tile - r.tile_lo);
   return r;
 }
-// sigmoid of a score given in base-2 units (x * log2(e)): 1 / (1 + 2^-v); -inf gives 0
-__device__ __forceinline__ float sigmoid2(float v) { return __frcp_rn(1.0f + exp2f(-v)); }
+// sigmoid of a score given in base-2 units (x * log2(e)): 1 / (1 + 2^-v) from the special-function unit's 2^x and 1/x (each
+// within two units of the last place; the weight is rounded to bfloat16 next); -inf gives 0
+__device__ __forceinline__ float sigmoid2(float v) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-v));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
 // the first key that a query at position p sees
 __device__ __forceinline__ int first_seen(int p, int window, int chunk) {
   int lo = window > 0 ? max(0, p - window + 1) : 0;

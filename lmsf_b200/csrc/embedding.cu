@@ -45,7 +45,7 @@ __global__ void embedding_scaled_kernel(T* __restrict__ out, const T* __restrict
 // request's first token.  The token before a portion's first token is the request's state: last[slot], one int32 per state
 // slot.  The block of a portion's first token reads it and then stores the portion's last token there; no other block touches
 // that slot, so the launch needs no second pass.  One block per token.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void embedding_pairs_kernel(float* __restrict__ out, const T* __restrict__ table, const T* __restrict__ pairs,
                                        const int* __restrict__ ids, const int* __restrict__ positions,
                                        const int* __restrict__ token_seq, const int* __restrict__ cu_q,
@@ -76,7 +76,18 @@ __global__ void embedding_pairs_kernel(float* __restrict__ out, const T* __restr
   const T* src = table + (size_t)(ok ? id : 0) * hidden;
   const T* pr = pairs + (size_t)(ok ? row : buckets) * hidden;
   float* dst = out + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? fmaf(to_f32(src[i]), scale, to_f32(pr[i])) : 0.f;
+  if constexpr (VEC) {   // four values an access: widths that 4 divides, aligned tables
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float a[4], b[4], r[4];
+      ld4(src + i, a);
+      ld4(pr + i, b);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) r[k] = ok ? fmaf(a[k], scale, b[k]) : 0.f;
+      st4(dst + i, r);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? fmaf(to_f32(src[i]), scale, to_f32(pr[i])) : 0.f;
+  }
 }
 
 // token_ids[dst[i]] = source[src[i]] for every i with dst[i] >= 0: puts tokens that were sampled on the device
@@ -147,14 +158,13 @@ LMSF_API int lmsf_embedding_pairs(float* out, const void* table, const void* pai
     LMSF_REFUSE("embedding: the pair index overflows 64 bits");
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = hidden >= 1024 ? 256 : 128;
-  if (dtype == LMSF_F32)
-    embedding_pairs_kernel<float><<<n_tokens, threads, 0, s>>>(out, (const float*)table, (const float*)pairs, ids, positions,
-                                                               token_seq, cu_q, state_slot, last, hidden, vocab, buckets,
-                                                               mul_prev, mul_cur, scale, error_flag);
-  else if (dtype == LMSF_BF16)
-    embedding_pairs_kernel<bf16><<<n_tokens, threads, 0, s>>>(out, (const bf16*)table, (const bf16*)pairs, ids, positions,
-                                                              token_seq, cu_q, state_slot, last, hidden, vocab, buckets,
-                                                              mul_prev, mul_cur, scale, error_flag);
+  const size_t esize = dtype == LMSF_F32 ? 4 : 2;
+  const bool vec = hidden % 4 == 0 && (uintptr_t)out % 16 == 0 && ((uintptr_t)table | (uintptr_t)pairs) % (4 * esize) == 0;
+#define LMSF_EP(T, V) embedding_pairs_kernel<T, V><<<n_tokens, threads, 0, s>>>(out, (const T*)table, (const T*)pairs, ids, positions, \
+    token_seq, cu_q, state_slot, last, hidden, vocab, buckets, mul_prev, mul_cur, scale, error_flag)
+  if (dtype == LMSF_F32) { if (vec) LMSF_EP(float, true); else LMSF_EP(float, false); }
+  else if (dtype == LMSF_BF16) { if (vec) LMSF_EP(bf16, true); else LMSF_EP(bf16, false); }
   else LMSF_REFUSE("embedding: unknown dtype code %d", dtype);
+#undef LMSF_EP
   return LMSF_LAUNCH_STATUS();
 }

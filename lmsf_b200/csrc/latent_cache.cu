@@ -153,6 +153,23 @@ __global__ void value_gate_kernel(T* __restrict__ x, long long x_stride, const T
   }
 }
 
+// the same, four values a thread and access: sizes that 4 divides, aligned rows
+template <typename T>
+__global__ void value_gate4_kernel(T* __restrict__ x, long long x_stride, const T* __restrict__ gate, long long gate_stride,
+                                   int heads, int head_dim, int value_dim) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 4; i < heads * value_dim; i += blockDim.x * 4) {
+    const int h = i / value_dim, d = i - h * value_dim;
+    float g[4], v[4];
+    ld4(gate + (size_t)t * gate_stride + i, g);
+    T* p = x + (size_t)t * x_stride + (size_t)h * head_dim + d;
+    ld4(p, v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] *= 1.0f / (1.0f + expf(-g[k]));
+    st4(p, v);
+  }
+}
+
 }  // namespace lmsf
 
 LMSF_API int lmsf_value_gate(void* x, long long x_stride, const void* gate, long long gate_stride, int n, int heads,
@@ -162,6 +179,16 @@ LMSF_API int lmsf_value_gate(void* x, long long x_stride, const void* gate, long
   if (heads <= 0 || head_dim <= 0 || value_dim <= 0 || value_dim > head_dim)
     LMSF_REFUSE("value_gate: heads=%d head_dim=%d value_dim=%d", heads, head_dim, value_dim);
   cudaStream_t s = (cudaStream_t)stream;
+  if (value_dim % 4 == 0 && head_dim % 4 == 0 && (dtype == LMSF_F32 || dtype == LMSF_BF16)) {
+    if (dtype == LMSF_F32 && rows_take4<float>(x, 4, x_stride) && rows_take4<float>(gate, 4, gate_stride)) {
+      value_gate4_kernel<float><<<n, 256, 0, s>>>((float*)x, x_stride, (const float*)gate, gate_stride, heads, head_dim, value_dim);
+      return LMSF_LAUNCH_STATUS();
+    }
+    if (dtype == LMSF_BF16 && rows_take4<bf16>(x, 4, x_stride) && rows_take4<bf16>(gate, 4, gate_stride)) {
+      value_gate4_kernel<bf16><<<n, 256, 0, s>>>((bf16*)x, x_stride, (const bf16*)gate, gate_stride, heads, head_dim, value_dim);
+      return LMSF_LAUNCH_STATUS();
+    }
+  }
   if (dtype == LMSF_F32) value_gate_kernel<float><<<n, 256, 0, s>>>((float*)x, x_stride, (const float*)gate, gate_stride, heads, head_dim, value_dim);
   else if (dtype == LMSF_BF16) value_gate_kernel<bf16><<<n, 256, 0, s>>>((bf16*)x, x_stride, (const bf16*)gate, gate_stride, heads, head_dim, value_dim);
   else LMSF_REFUSE("value_gate: unknown dtype code %d", dtype);

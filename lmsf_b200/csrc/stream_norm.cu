@@ -410,6 +410,38 @@ LMSF_API int lmsf_stream_concat(void* out, const float* a, const float* b, int n
 // token; the slot holds h's values exactly (float32 of what h stores), so a cut changes no bit.
 namespace lmsf {
 
+// the same, four values a thread and access: widths that 4 divides, aligned rows
+template <typename T>
+__global__ void token_shift4_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ mix,
+                                    float* __restrict__ state, const int* __restrict__ positions,
+                                    const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                                    const int* __restrict__ state_slot, int hidden) {
+  const int t = blockIdx.x;
+  const int seq = token_seq[t];
+  const bool starts = t == cu_q[seq];
+  const bool zero = positions[t] == 0;
+  const T* cur = h + (size_t)t * hidden;
+  T* dst = out + (size_t)t * hidden;
+  float* slot = starts ? state + (size_t)state_slot[seq] * hidden : nullptr;
+  const T* last = starts ? h + (size_t)(cu_q[seq + 1] - 1) * hidden : nullptr;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float c[4], b[4] = {0.f, 0.f, 0.f, 0.f}, m[4], o[4];
+    ld4(cur + i, c);
+    ld4(mix + i, m);
+    if (starts) {
+      if (!zero) ld4(slot + i, b);
+      float l[4];
+      ld4(last + i, l);
+      st4(slot + i, l);
+    } else if (!zero) {
+      ld4(cur - hidden + i, b);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = fmaf(b[k] - c[k], m[k], c[k]);
+    st4(dst + i, o);
+  }
+}
+
 template <typename T>
 __global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ mix,
                                    float* __restrict__ state, const int* __restrict__ positions,
@@ -451,6 +483,13 @@ LMSF_API int lmsf_token_shift(void* out, const void* h, const float* mix, float*
   if (hidden <= 0 || out == h) LMSF_REFUSE("token_shift: hidden=%d, and out must not be h", hidden);
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = hidden >= 1024 ? 256 : 128;
+  const bool f32 = dtype == LMSF_F32;
+  if ((dtype == LMSF_F32 || dtype == LMSF_BF16) && hidden % 4 == 0 && (uintptr_t)mix % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+      ((uintptr_t)out | (uintptr_t)h) % (f32 ? 16 : 8) == 0) {
+    if (f32) token_shift4_kernel<float><<<n, threads, 0, s>>>((float*)out, (const float*)h, mix, state, positions, token_seq, cu_q, state_slot, hidden);
+    else token_shift4_kernel<bf16><<<n, threads, 0, s>>>((bf16*)out, (const bf16*)h, mix, state, positions, token_seq, cu_q, state_slot, hidden);
+    return LMSF_LAUNCH_STATUS();
+  }
   if (dtype == LMSF_F32)
     token_shift_kernel<float><<<n, threads, 0, s>>>((float*)out, (const float*)h, mix, state, positions, token_seq, cu_q, state_slot, hidden);
   else if (dtype == LMSF_BF16)
