@@ -176,6 +176,8 @@ struct Unit {
   // the unit's tiles are 0 .. n_first - 1 (kept first keys behind the window) and then tile_begin ..; place j of that list
   int n_first;
   __device__ __forceinline__ int phys(int j) const { return j < n_first ? j : tile_begin + (j - n_first); }
+  // kKeep: the build that knows kept first keys; the other has kf = 0 folded into everything that follows from it
+  template <bool kKeep>
   __device__ __forceinline__ Item item(const Args& a, int x) const {
     Item i;
     i.head = head0 + (two_heads ? x : 0);
@@ -185,12 +187,12 @@ struct Unit {
     i.lo = first_seen(start + i.q0, a.window, a.x.chunk);       // the first row's: later rows start no earlier
     i.tb = i.lo / BN;
     i.te = (i.hi + BN - 1) / BN;
-    i.kf = a.x.keep_first > 0 ? min((a.x.keep_first + BN - 1) / BN, i.tb) : 0;
+    i.kf = (kKeep && a.x.keep_first > 0) ? min((a.x.keep_first + BN - 1) / BN, i.tb) : 0;
     return i;
   }
   // kLeft: the kernel is built twice, for even groups of heads (no unit of a head that is left over: the plain
   // numbering, which is also a little faster) and for odd ones
-  template <bool kLeft>
+  template <bool kLeft, bool kKeep>
   __device__ __forceinline__ void load(const Args& a, int unit, const UnitMap& m) {
     int tile, pair;
     if (!kLeft || unit < m.n_full) {
@@ -214,7 +216,7 @@ struct Unit {
     // A head that is left over takes two query tiles: this one and the 128 tokens behind it.
     empty = !two_heads && (q0 & (2 * BM - 1)) != 0;
     two = two_heads || q0 + BM < n;                             // the unit has a second item
-    const Item i0 = item(a, 0), i1 = item(a, 1);
+    const Item i0 = item<kKeep>(a, 0), i1 = item<kKeep>(a, 1);
     lo = i0.lo;                                                 // the second item is never behind the first
     hi = two ? i1.hi : i0.hi;
     tile_begin = i0.tb;
@@ -224,7 +226,10 @@ struct Unit {
   }
 };
 
-template <bool kLeft>
+// kSig: sigmoid weights (a second build of the softmax warps' loop, so that the softmax form carries no test of it).  kKeep: a
+// window that keeps the request's first keys (a list of tiles with a gap); without it every count of kept tiles is a constant 0
+// and the kernel is the one it was before it learnt of them.  Built: plain, kKeep, and kSig with kKeep.
+template <bool kLeft, bool kSig, bool kKeep>
 __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map,
                                                                       const __grid_constant__ CUtensorMap q_map) {
   extern __shared__ unsigned char smem_raw[];
@@ -337,7 +342,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
       Unit u = {};
-      u.template load<kLeft>(a, unit, um);
+      u.template load<kLeft, kKeep>(a, unit, um);
       if (u.empty) continue;
       const int* table = a.block_table + (size_t)u.seq * a.max_blocks;
       if (a.use_tma) {
@@ -371,7 +376,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         for (int t = 0; t < u.n_tiles; ++t) {
           const int g = tiles_before + t, s = g % kStages;
           if (g >= kStages && !mbar_wait_f(empty(s), (uint32_t)((g / kStages - 1) & 1), failed)) { ok = false; break; }
-          gather_tile(ring + s * kKBytes, a.kv, table, a.max_blocks, u.kvh, is_v, u.phys(t) * BN, u.lo, u.hi, a.x.keep_first, lane);
+          gather_tile(ring + s * kKBytes, a.kv, table, a.max_blocks, u.kvh, is_v, u.phys(t) * BN, u.lo, u.hi, kKeep ? a.x.keep_first : 0, lane);
           cp_async_arrive(full(s));
         }
       }
@@ -398,9 +403,9 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
       Unit u = {};
-      u.template load<kLeft>(a, unit, um);
+      u.template load<kLeft, kKeep>(a, unit, um);
       if (u.empty) continue;
-      const Item it0 = u.item(a, 0), it1 = u.item(a, 1);
+      const Item it0 = u.template item<kKeep>(a, 0), it1 = u.template item<kKeep>(a, 1);
       const int nx = u.two ? 2 : 1;
       const int n_tiles = u.n_tiles;
       // whether item x has tile t (a tile's number among the keys, not its place in the unit's list)
@@ -517,12 +522,12 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const int unit = unit_of(pass);
       if (unit >= n_units) break;
       Unit u = {};
-      u.template load<kLeft>(a, unit, um);
+      u.template load<kLeft, kKeep>(a, unit, um);
       if (u.empty) continue;
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
         if (x == 1 && !u.two) continue;
-        const Item me = u.item(a, x);
+        const Item me = u.template item<kKeep>(a, x);
         // The item's scores of the unit before are complete: its queries may be overwritten.  And its softmax warps
         // have taken that unit's note: q_full[x] has two kinds of waiters, the issuing warp and the softmax warps, and
         // must not complete a second phase before both have seen the first (an item with a single tile in a unit
@@ -575,27 +580,25 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
       const volatile UnitNote* note = &notes[x][my_units_before & 1];
       if (note->last) break;
       mbar_arrive(taken(x));
-      struct { int rows, tb, te, kf; } me = {note->rows, note->tb, note->te, note->kf};
-      const int u_first = note->n_first, u_tile_begin = note->tile_begin, u_tiles_before = note->tiles_before;
+      // (kf: the item's kept first tiles come first, then its window's; tb_rest: the window's first tile less kf, so that
+      // place j of the item's list is tile j below kf and tile tb_rest + j from there on)
+      struct { int rows, kf, tb_rest; } me = {note->rows, kKeep ? note->kf : 0, note->tb - (kKeep ? note->kf : 0)};
       const int q_pos0 = note->start + note->q0;                    // position of the item's first query
       const int u_lo = note->lo, u_hi = note->hi;
       const bool row_ok = row < me.rows;
       const int pos = q_pos0 + min(row, me.rows - 1);                // this thread's query position
       const int row_lo = first_seen(pos, a.window, a.x.chunk);
-      const int keep = a.x.keep_first;
-      const bool sig = a.x.sigmoid != 0;                             // sigmoid weights: no maximum, no rescaling, no denominator
-      const float hb2 = a.x.head_bias ? a.x.head_bias[note->head] * kLog2e : 0.f;
+      constexpr bool sig = kSig;                                     // sigmoid weights: no maximum, no rescaling, no denominator
+      // the head's bias on the scores (with sigmoid weights only: a softmax is refused one by the launcher of this kernel)
+      const float hb2 = (sig && a.x.head_bias) ? a.x.head_bias[note->head] * kLog2e : 0.f;
       float m_run = sig ? 0.f : -INFINITY, l_run = 0.f;
-      const int my_tiles = me.kf + me.te - me.tb;
+      const int my_tiles = note->te - me.tb_rest;
       for (int j = 0; j < my_tiles; ++j) {                           // j counts this item's tiles
         // S of the tile is complete, and with it every product issued before it: P V of the tile before too
         ok = mbar_wait_f(s_full(x), (uint32_t)((my_tiles_before + j) & 1), failed);
         if (!ok) break;
         tc_fence_after();
-        const int tile = j < me.kf ? j : me.tb + (j - me.kf);       // the tile's number among the keys
-        const int key0 = tile * BN;
-        // the tile counted over the block's units: its stage
-        const int ju = u_tiles_before + (tile < u_first ? tile : u_first + tile - u_tile_begin);
+        const int key0 = (j < me.kf ? j : me.tb_rest + j) * BN;     // the tile's first key
         // Only tiles that reach past some row's position (the diagonal) or before its window need the mask;
         // the test is the same for the whole group of warps.
         // (the item's last row starts latest: a tile that begins before that start has keys some row does not see)
@@ -627,7 +630,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
 #pragma unroll
           for (int i = 0; i < BN; ++i) {
             const int key = key0 + i;
-            if ((key > pos) | ((key < row_lo) & (key >= keep))) sc[i] = -INFINITY;
+            if ((key > pos) | ((key < row_lo) & (key >= (kKeep ? a.x.keep_first : 0)))) sc[i] = -INFINITY;
           }
         }
         // four chains of three-input maxima: 128 values in 16 dependent steps
@@ -642,7 +645,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         }
         float mx = fmaxf(fmax3(mx0, mx1, mx2), fmax3(mx3, sc[BN - 4], sc[BN - 3]));
         mx = fmax3(mx, sc[BN - 2], sc[BN - 1]);
-        mx = fmaf(mx, sl2, hb2);                                  // scores enter the exponent as s * scale * log2(e) + the head's bias
+        mx *= sl2;                                                // scores enter the exponent as s * scale * log2(e)
         float alpha = 1.f;
         const bool grow = !sig && mx > m_run + kRescaleThreshold; // also true for the first keys a row sees
         if (grow) {
@@ -663,6 +666,11 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         if (key0 < u_lo || key0 + BN > u_hi) {
           // rows of v whose keys no query of the tile sees hold whatever their page holds: clear them, so that
           // their zero weights cannot meet a value that is not finite (both items' warps do, with the same zeros)
+          // the tile counted over the block's units, which names its stage: a kept tile's place in the unit's list is its
+          // number (the list starts at tile 0 then); a tile of the window comes n_first - tile_begin places after its number
+          const int tile = key0 / BN;
+          const int ju = note->tiles_before + (j < me.kf ? tile : (kKeep ? note->n_first : 0) + tile - note->tile_begin);
+          const int keep = kKeep ? a.x.keep_first : 0;
           const uint32_t v = sV + (ju % kStages) * kKBytes;
           const int r_lo = u_lo - key0, r_hi = u_hi - key0;
           ok = mbar_wait_f(v_full(ju % kStages), (uint32_t)((ju / kStages) & 1), failed);   // the tile's v has landed
@@ -675,13 +683,14 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
           fence_async_smem();
         }
         // P as bfloat16 pairs over the first 64 columns of S: keys 2c and 2c + 1 in column c
-        const float neg_m = (m_run == -INFINITY ? 0.f : -m_run) + hb2;
+        const float neg_m = sig ? hb2 : (m_run == -INFINITY ? 0.f : -m_run);
         // The scaling, the subtraction of the maximum and the row sums are packed (two values per instruction); the
         // exponentials come from the special-function unit.  (Tried and slower on this kernel: a share of the
         // exponentials by a polynomial on the FMA pipe, and exponentials of bfloat16 pairs; the softmax warps are
         // bound by the instructions they issue, not by that unit.)  The first 64 keys' P is handed to the issuing warp
         // while the other 64 are computed.
-        const uint64_t sl2_2 = pk2(sl2, sl2), neg_m2 = pk2(neg_m, neg_m);
+        // (sigmoid weights: the exponent is negated here, 2^-(s * scale * log2(e) + bias), so that the loop needs no negation)
+        const uint64_t sl2_2 = sig ? pk2(-sl2, -sl2) : pk2(sl2, sl2), neg_m2 = sig ? pk2(-neg_m, -neg_m) : pk2(neg_m, neg_m);
         uint64_t lsum = pk2(0.f, 0.f);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -691,9 +700,9 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
             const uint64_t x2 = fma2(pk2(sc[h * 64 + 2 * i], sc[h * 64 + 2 * i + 1]), sl2_2, neg_m2);
             float p0, p1, x0, x1;
             upk2(x2, x0, x1);
-            if (sig) {                                            // 1 / (1 + 2^-x); a masked score (-inf) gives 0
-              p0 = rcp_approx(1.0f + ex2_approx(-x0));
-              p1 = rcp_approx(1.0f + ex2_approx(-x1));
+            if constexpr (sig) {                                  // 1 / (1 + 2^-x), x0 = -x; a masked score (-inf) gives 0
+              p0 = rcp_approx(1.0f + ex2_approx(x0));
+              p1 = rcp_approx(1.0f + ex2_approx(x1));
             } else {
               p0 = ex2_approx(x0);
               p1 = ex2_approx(x1);
@@ -816,6 +825,7 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
   if ((r1 == nullptr) != (r2 == nullptr) || chunk < 0 || (r1 && !(scale > 0.f)))
     LMSF_REFUSE("attention_prefill_tc: the distance bias takes both constants and a positive scale; chunk >= 0");
   if (sigmoid && sinks) LMSF_REFUSE("attention_prefill_tc: sinks belong to a softmax, not to sigmoid weights");
+  if (!sigmoid && head_bias) LMSF_REFUSE("attention_prefill_tc: a bias per head is taken with sigmoid weights only");
   a.x = ScoreExtras{chunk, r1, r2, sinks, (window > 0 && keep_first > 0) ? keep_first : 0, sigmoid ? 1 : 0, head_bias};
   // pages of 8 keys and more come by tensor-map copies (a box of rows_box keys starts on a 1024-byte
   // boundary of the swizzled tile); smaller pages by cp.async
@@ -847,12 +857,17 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
   if (left && n_tiles > kMaxLeadTiles)
     LMSF_REFUSE("attention_prefill_tc: with an odd number of query heads per kv head a launch takes %d query tiles at most, not %d",
                 kMaxLeadTiles, n_tiles);
-  void (*kernel)(const Args, const CUtensorMap, const CUtensorMap) = left ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
-  static bool configured[2] = {false, false};
-  if (!configured[left]) {
+  const bool sig = a.x.sigmoid != 0;
+  const int form = sig ? 2 : (a.x.keep_first > 0 ? 1 : 0);
+  void (*kernel)(const Args, const CUtensorMap, const CUtensorMap) =
+      form == 2 ? (left ? prefill_tc_kernel<true, true, true> : prefill_tc_kernel<false, true, true>)
+      : form == 1 ? (left ? prefill_tc_kernel<true, false, true> : prefill_tc_kernel<false, false, true>)
+                  : (left ? prefill_tc_kernel<true, false, false> : prefill_tc_kernel<false, false, false>);
+  static bool configured[3][2] = {{false, false}, {false, false}, {false, false}};
+  if (!configured[form][left]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    configured[left] = true;
+    configured[form][left] = true;
   }
   // one block per SM at most (a block holds all of an SM's tensor memory); the blocks share the units out among them
   static int n_sms = 0;

@@ -54,7 +54,7 @@ def _nvcc() -> str:
 def _writable_dir(path: str) -> bool:
     try:
         os.makedirs(path, exist_ok=True)
-        probe = os.path.join(path, f".w{os.getpid()}")
+        probe = os.path.join(path, f".w{os.getpid()}_{threading.get_ident()}")
         with open(probe, "w"):
             pass
         os.remove(probe)
