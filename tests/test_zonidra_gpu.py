@@ -502,6 +502,63 @@ def test_greedy_generation_through_the_engine():
             toks.append(got)
 
 
+def test_preemption_by_recompute_rebuilds_pages_and_state():
+    """With few pages the youngest request is dropped and later recomputed from its prompt and its tokens so far: its pages,
+    its shift rows and its remembered token start again from nothing.  Greedy and seeded sampling give the tokens of a run with
+    room for all, synchronous or with steps launched ahead."""
+    from lmsf_b200 import LLM, SamplingParams
+    folder, _ = folder_of("X")
+    cfg = CONFIGS["X"]
+    prompts = [util.random_ids(n, cfg["vocab"], 20 + i) for i, n in enumerate([30, 25, 28, 20])]
+    sp = [SamplingParams(temperature=0.7 if i % 2 else 0.0, seed=5 + i, max_tokens=40, ignore_eos=True) for i in range(4)]
+    roomy = LLM(folder, dtype="float32", block_size=8, num_gpu_blocks=128, max_num_batched_tokens=32, max_num_seqs=4)
+    want = [o.outputs[0].token_ids for o in roomy.generate(prompt_token_ids=prompts, sampling_params=sp)]
+    assert roomy.engine.scheduler.num_preemptions == 0
+    for ahead in (True, False):
+        tight = LLM(folder, dtype="float32", block_size=8, num_gpu_blocks=14, max_num_batched_tokens=32, max_num_seqs=4,
+                    async_scheduling=ahead)
+        got = [o.outputs[0].token_ids for o in tight.generate(prompt_token_ids=prompts, sampling_params=sp)]
+        assert tight.engine.scheduler.num_preemptions > 0
+        assert got == want, ahead
+        tight.engine.cache.check_invariants()
+        assert all(tight.engine.cache.num_free_pages(g) == 14 for g in range(len(tight.engine.cache.groups)))
+
+
+def test_the_example_program_generates_with_the_design():
+    """bin/llm_engine_example as a process: a model folder and prompts in, one JSON line per request out; top-k sampling with a
+    seed gives the same tokens twice, and greedy tokens are the plain implementation's."""
+    import json
+    import os
+    import subprocess
+    import sys
+    folder, w = folder_of("Y")
+    cfg = CONFIGS["Y"]
+    prompts = [util.random_ids(n, cfg["vocab"], 90 + i) for i, n in enumerate([7, 33])]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(*options):
+        cmd = [sys.executable, os.path.join(root, "bin", "llm_engine_example"), "--model", folder, "--dtype", "float32",
+               "--block-size", "16", "--num-gpu-blocks", "32", "--max-num-seqs", "4", "--max-num-batched-tokens", "24",
+               "--max-tokens", "8", "--ignore-eos", *options]
+        for p in prompts:
+            cmd += ["--prompt-ids", ",".join(str(t) for t in p)]
+        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        lines = [json.loads(ln) for ln in proc.stdout.splitlines() if ln.startswith("{")]
+        return {d["request_id"]: d["token_ids"] for d in lines}
+
+    greedy = run("--temperature", "0")
+    for i, p in enumerate(prompts):
+        toks = list(p)
+        for got in greedy[i]:
+            lg = P.forward(cfg, w, toks, dtype=torch.float64)[-1]
+            nxt = int(lg.argmax())
+            assert got == nxt or float(lg[nxt] - lg[got]) <= 1e-4 * float(lg.abs().max())
+            toks.append(got)
+    sampled = run("--temperature", "0.8", "--top-k", "5", "--seed", "3")
+    assert sampled == run("--temperature", "0.8", "--top-k", "5", "--seed", "3") and sampled != greedy
+
+
 # ----------------------------------------------------------------------------- random configurations
 
 def random_config(seed):
