@@ -21,14 +21,14 @@ def zonidra_config(width, heads, kv_heads, dim, window, keep, experts, top, ff, 
     rot = {"dims": dim // 2, "base": 1.0e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
     mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": rot,
              "mask": {"size": window, "keep_first": keep}}
-    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "identity": 2, "scale": 2.5},
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "identity": 2, "scale": 2.0},
            "shared": {"ff": shared}}
     own = lambda mlp: {"type": "attention", "mixer": dict(mixer), "mlp": mlp}
     reads = lambda j, mlp: {"type": "attention", "mixer": dict(mixer, kv_from=j), "mlp": mlp}
     # four layers, as the models beside it: two with keys and values of their own and a dense feed-forward, each followed
     # by a layer that reads them and routes to experts
     return {"architecture": "Zonidra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
-            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 33, "mul_cur": 5}},
             "layers": [own({"kind": "dense", "ff": dense_ff}), reads(0, moe), own({"kind": "dense", "ff": dense_ff}), reads(2, moe)]}
 
 
@@ -76,7 +76,7 @@ def kernels_alone(pk, width=4096, heads=32, kv_heads=8, dim=128, window=1024, ke
     last = torch.zeros(2, 1, dtype=i32, device=dev)
     res = torch.empty(T, width, dtype=f32, device=dev)
     rec("embedding_pairs (two rows gathered, scaled sum in float32) 2048 x 4096",
-        tm.run(lambda: kernels.embedding_pairs(res, table, pairs, ids, pos, seq, cu, slot, last, buckets, 31, 7, 64.0, flag), 3, 10),
+        tm.run(lambda: kernels.embedding_pairs(res, table, pairs, ids, pos, seq, cu, slot, last, buckets, 33, 5, 64.0, flag), 3, 10),
         bytes_=T * width * (2 + 2 + 4), like="embedding below")
     xb = torch.empty(T, width, dtype=bf, device=dev)
     rec("embedding (Llama: one row gathered) 2048 x 4096", tm.run(lambda: kernels.embedding(xb, table, ids, flag), 3, 10),
@@ -104,13 +104,13 @@ def kernels_alone(pk, width=4096, heads=32, kv_heads=8, dim=128, window=1024, ke
     rid, rw = torch.empty(T, top, dtype=i32, device=dev), torch.empty(T, top, dtype=f32, device=dev)
     corr = rnd(R, dtype=f32, scale=0.05)
     rec(f"moe_topk_softmax_all (softmax over {R} outputs, choice with a correction) 2048 tokens",
-        tm.run(lambda: kernels.moe_topk_softmax_all(rid, rw, logits, corr, R, 2.5), 3, 10), bytes_=T * (R + 1) * 4 + T * top * 8,
+        tm.run(lambda: kernels.moe_topk_softmax_all(rid, rw, logits, corr, R, 2.0), 3, 10), bytes_=T * (R + 1) * 4 + T * top * 8,
         like="moe_topk below")
     rec(f"moe_topk (Vufolorn: top of {experts}, softmax over the chosen) 2048 tokens",
         tm.run(lambda: kernels.moe_topk(rid, rw, logits, corr[:experts].contiguous(), experts), 3, 10), bytes_=T * (R + 1) * 4 + T * top * 8)
     pairs_n = T * top
     down = rnd(pairs_n, width, dtype=f32)
-    kernels.moe_topk_softmax_all(rid, rw, logits, corr, R, 2.5)
+    kernels.moe_topk_softmax_all(rid, rw, logits, corr, R, 2.0)
     pair_row = torch.randperm(pairs_n, device=dev, generator=g).to(i32).view(T, top)
     pair_row = torch.where(rid >= experts, torch.full_like(pair_row, -1), pair_row)
     shared, out = rnd(T, width), torch.empty(T, width, dtype=bf, device=dev)

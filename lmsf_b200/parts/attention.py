@@ -163,7 +163,8 @@ class PagedAttention(Mixer):
                            keep_first=self.cache_keep_first if self.cache_window else 0)
 
     def activation_width(self) -> int:
-        return 2 * self.q_size + 2 * self.kv_size           # q, k, v and the attention's output
+        # q, k, v and the attention's output; the logits of a gate per element ride in the merged product
+        return 2 * self.q_size + 2 * self.kv_size + (self.num_heads * self.value_dim if self.value_gate else 0)
 
     def prepare(self, dtype, device) -> None:
         if self.position_encoding is not None:

@@ -62,9 +62,9 @@ def test_the_pair_embedding_remembers_the_token_before_a_portion(dtype, vocab, D
     from lmsf_b200.parts.embedding import PairTokenEmbedding
     g = torch.Generator().manual_seed(vocab)
     tdt = TDT[dtype]
-    cfg = {"embedding": embedding(2.5, buckets, mp, mc)}
+    cfg = {"embedding": embedding(1.75, buckets, mp, mc)}
     W = {"embed": torch.randn(vocab, D, generator=g).to(tdt), "bigram": torch.randn(buckets + 1, D, generator=g).to(tdt)}
-    part = PairTokenEmbedding(vocab, D, buckets, mp, mc, scale=2.5)
+    part = PairTokenEmbedding(vocab, D, buckets, mp, mc, scale=1.75)
     part.set_weights({"weight": dev(W["embed"]), "pairs": dev(W["bigram"])})
     state = torch.full((4, 1), 7, dtype=torch.int32, device=DEV)              # stale tokens of whoever had the slots before
     toks = {0: util.random_ids(23, vocab, 1), 1: util.random_ids(17, vocab, 2)}
@@ -252,7 +252,7 @@ def run_in_cuts(parts, hs, cuts, bs, tdt, pages=40, seed=9):
 SHAPES = [  # heads, kv heads, dim, vdim, window, keep_first, rotation, page size
     (4, 2, 24, 16, 21, 3, rotation(8, 300.0, (3.0, 1.0, 5.0, 40)), 8),
     (4, 1, 64, 48, 50, 0, rotation(64, 10000.0), 16),
-    (2, 2, 128, 64, 136, 4, rotation(32, 1.0e6, (4.0, 1.0, 4.0, 1024)), 16),
+    (2, 2, 128, 64, 150, 6, rotation(48, 5.0e5, (2.0, 1.0, 8.0, 512)), 16),
     (3, 3, 40, 24, None, 0, None, 16),
     (6, 2, 20, 80, 7, 1, rotation(2, 50.0), 16),
     (2, 1, 64, 64, 70, 130, rotation(16, 500.0), 32),
@@ -565,7 +565,7 @@ def random_config(seed):
     """Sizes that are no multiples of anything in particular, every optional piece present or absent by chance, readers of
     earlier layers with masks of their own, values that a hand-made configuration tends to make equal or 1."""
     rng = random.Random(seed)
-    width = rng.choice([36, 50, 56, 72, 104, 136])
+    width = rng.choice([36, 50, 56, 72, 104, 140])
     layers, owners = [], []
     for i in range(rng.randint(1, 5)):
         window = rng.choice([None, 1, 5, 16, 31, 64, 100])
@@ -588,12 +588,12 @@ def random_config(seed):
             mlp = dense(rng.choice([8, 20, 44, 100]))
         else:
             experts, identity = rng.randint(1, 7), rng.choice([0, 0, 1, 3])
-            mlp = moe(experts, rng.randint(1, experts + identity), rng.choice([8, 16, 24, 40]), identity, rng.choice([1.0, 2.5, 0.5]),
+            mlp = moe(experts, rng.randint(1, experts + identity), rng.choice([8, 16, 24, 40]), identity, rng.choice([1.0, 2.0, 0.5]),
                       rng.choice([0, 8, 24]))
         layers.append(with_mlp(mixer, mlp))
     vocab = rng.choice([61, 128, 257])
     return {"architecture": "Zonidra", "vocab": vocab, "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])},
-            "embedding": embedding(rng.choice([1.0, 4.0, 12.0]), rng.choice([1, 7, 64, 509]), rng.randint(0, 40), rng.randint(0, 40)),
+            "embedding": embedding(rng.choice([1.0, 4.0, 12.0]), rng.choice([1, 7, 64, 521]), rng.randint(0, 40), rng.randint(0, 40)),
             "layers": layers}
 
 

@@ -51,13 +51,13 @@ CONFIGS = {
     "Y": {"architecture": "Zonidra", "vocab": 130, "width": 64, "norm": {"eps": 1e-6}, "embedding": embedding(1.0, 1, 0, 1),
           "layers": [with_mlp(attention(6, 1, 16, 16, 0.4, None, 0, rotation(16, 10000.0)), moe(3, 3, 16)),
                      with_mlp(attention(6, 1, 16, 16, 0.2, 17, 2, rotation(16, 10000.0), kv_from=0), None),
-                     with_mlp(attention(3, 3, 40, 24, 0.15), moe(1, 1, 32, 1, 2.5, 8))]},
+                     with_mlp(attention(3, 3, 40, 24, 0.15), moe(1, 1, 32, 1, 3.0, 8))]},
     # head sizes of the tensor-core kernels with windows longer than a tile; more identity outputs than experts; two
     # readers of one layer
-    "Z": {"architecture": "Zonidra", "vocab": 300, "width": 96, "norm": {"eps": 1e-5}, "embedding": embedding(8.0, 101, 31, 7),
-          "layers": [with_mlp(attention(4, 2, 64, 64, 0.125, 150, 4, rotation(32, 1.0e6, (4.0, 1.0, 4.0, 64))), dense(40)),
-                     with_mlp(attention(4, 2, 64, 64, 0.2, 70, 130, rotation(32, 1.0e6, (4.0, 1.0, 4.0, 64)), kv_from=0), moe(2, 2, 32, 3, 0.7)),
-                     with_mlp(attention(4, 2, 64, 64, 0.1, 300, 0, rotation(32, 1.0e6, (4.0, 1.0, 4.0, 64)), kv_from=0), moe(7, 1, 8, 0, 1.0, 24)),
+    "Z": {"architecture": "Zonidra", "vocab": 300, "width": 96, "norm": {"eps": 1e-5}, "embedding": embedding(8.0, 101, 29, 11),
+          "layers": [with_mlp(attention(4, 2, 64, 64, 0.125, 150, 6, rotation(32, 5.0e5, (6.0, 1.0, 3.0, 64))), dense(40)),
+                     with_mlp(attention(4, 2, 64, 64, 0.2, 70, 130, rotation(32, 5.0e5, (6.0, 1.0, 3.0, 64)), kv_from=0), moe(2, 2, 32, 3, 0.7)),
+                     with_mlp(attention(4, 2, 64, 64, 0.1, 300, 0, rotation(32, 5.0e5, (6.0, 1.0, 3.0, 64)), kv_from=0), moe(7, 1, 8, 0, 1.0, 24)),
                      with_mlp(attention(2, 1, 128, 48, 0.09, 129, 1, rotation(2, 100.0)), dense(72))]},
 }
 BLOCK = {"X": 8, "Y": 16, "Z": 16}
